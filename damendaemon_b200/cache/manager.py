@@ -49,13 +49,35 @@ class PagedKeyValues(PagedNeed):
     kv_heads: int
     head_dim: int
     window: Optional[int] = None     # None: every earlier key stays; n: the last n keys
+    value_dim: Optional[int] = None  # size of a value head where it differs from head_dim
+    chunk: Optional[int] = None      # n: positions come in chunks of n from the start of the sequence and a query sees
+                                     # its own chunk only, so a page that lies wholly before the newest chunk is done with
 
     def page_shape(self, page_size):
-        return (2, self.kv_heads, page_size, self.head_dim)      # key plane and value plane, head-major inside a page
+        if self.value_dim is None or self.value_dim == self.head_dim:
+            return (2, self.kv_heads, page_size, self.head_dim)      # key plane and value plane, head-major inside a page
+        # a key plane [kv_heads, page, head_dim] followed by a value plane [kv_heads, page, value_dim]
+        return (self.kv_heads * page_size * (self.head_dim + self.value_dim),)
+
+    def first_needed(self, length: int) -> int:
+        """The first position a query at position ``length`` or later can still see."""
+        first = 0
+        if self.window is not None:
+            first = max(first, length - self.window + 1)
+        if self.chunk is not None:
+            first = max(first, length - length % self.chunk)
+        return first
+
+    def span(self) -> Optional[int]:
+        """Most positions before a query that it can see and that must be kept (None: all of them)."""
+        spans = [n - 1 for n in (self.window, self.chunk) if n is not None]
+        return min(spans) if spans else None
 
     @property
     def label(self):
-        return f"kv{self.kv_heads}x{self.head_dim}"
+        v = "" if self.value_dim in (None, self.head_dim) else f"v{self.value_dim}"
+        c = "" if self.chunk is None else f".c{self.chunk}"
+        return f"kv{self.kv_heads}x{self.head_dim}{v}{c}"
 
 
 @dataclass(frozen=True)
@@ -81,6 +103,9 @@ class CacheGroup:
 
     def first_needed_block(self, length: int) -> int:
         """Blocks before this one hold only keys that no later query can see."""
+        first_needed = getattr(self.need, "first_needed", None)
+        if first_needed is not None:
+            return max(0, first_needed(length)) // self.pool.page_size
         if self.need.window is None:
             return 0
         return max(0, length - self.need.window + 1) // self.pool.page_size
@@ -92,9 +117,11 @@ class CacheGroup:
     def peak_pages(self, total_tokens: int, max_step_tokens: int) -> int:
         """Most pages a request of total_tokens can hold at once (for promises)."""
         full = self.pool.pages_for(total_tokens)
-        if self.need.window is None:
+        span = self.need.span() if hasattr(self.need, "span") else \
+            (None if self.need.window is None else self.need.window - 1)
+        if span is None:
             return full
-        return min(full, self.pool.pages_for(self.need.window - 1 + max_step_tokens) + 1)
+        return min(full, self.pool.pages_for(span + max_step_tokens) + 1)
 
 
 class CacheManager:

@@ -1,4 +1,5 @@
 from .reader import ConfigError, parse_config_text, read_config_file
+from .bonatar import BonatarConfig
 from .gpt2 import Gpt2Config
 
-__all__ = ["ConfigError", "parse_config_text", "read_config_file", "Gpt2Config"]
+__all__ = ["ConfigError", "parse_config_text", "read_config_file", "Gpt2Config", "BonatarConfig"]

@@ -7,8 +7,13 @@
 // partial results merged by their log-sum-exp).
 //
 // Query token t at position p of entry e sees keys lo..p, lo = max(0, p - window + 1)
-// with a window, else 0. Key j lives in page block_table[e][j / page_size] of the
-// layer's cache [n_pages, 2, kv_heads, page_size, head_dim]. With n_splits > 1 the
+// with a window, else 0; with a chunk size c (keys and queries in chunks of c positions counted
+// from the start of the sequence, nothing seen across a chunk's border) lo is at least p - p % c.
+// Key j lives in page block_table[e][j / page_size] of the
+// layer's cache [n_pages, 2, kv_heads, page_size, head_dim]; a value head may have a size dv of its
+// own, a page is then its key plane [kv_heads, page_size, head_dim] followed by its value plane
+// [kv_heads, page_size, dv]. An optional gate, one number per token and head (row views like q),
+// multiplies a head's output by its logistic function, in float32, before the result is rounded. With n_splits > 1 the
 // key range is cut in n_splits pieces whose (max, sum, unnormalised output) go to
 // scratch and dd_attention_merge combines them.
 #include "common.cuh"
@@ -47,7 +52,8 @@ attention_rows_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
                       const int* __restrict__ block_table, int max_blocks,
                       T* __restrict__ out, int out_stride, float* __restrict__ part_o, float* __restrict__ part_ml,
                       int n_tokens, int H, int KH, int d, int P, int n_pages, int window, float scale,
-                      int n_splits, int* __restrict__ error_flag) {
+                      int n_splits, int* __restrict__ error_flag, int dv, int chunk,
+                      const T* __restrict__ gate, int gate_stride) {
     extern __shared__ float q_smem[];
     dd_launch_dependents();
     dd_grid_wait();
@@ -59,7 +65,8 @@ attention_rows_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
     const int t = (int)(item / ((long long)n_splits * H));
     const int pos = tok_pos[t];
     const int kh = h / (H / KH);
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (chunk > 0) lo = max(lo, pos - pos % chunk);
     const int hi = pos + 1;
     int per = (hi - lo + n_splits - 1) / n_splits;
     per = (per + 31) / 32 * 32;
@@ -72,7 +79,9 @@ attention_rows_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
     __syncwarp();
 
     const int* bt = block_table + (size_t)tok_entry[t] * max_blocks;
-    const size_t head_plane = (size_t)P * d;
+    const size_t key_plane = (size_t)P * d, value_plane = (size_t)P * dv;
+    const size_t page_elems = (size_t)KH * (key_plane + value_plane);
+    const bool wide = d % Vec<T>::N == 0 && page_elems % Vec<T>::N == 0;   // key rows are whole, aligned 16-byte pieces
     float m = -CUDART_INF_F, l = 0.f, o[DPL];
 #pragma unroll
     for (int i = 0; i < DPL; ++i) o[i] = 0.f;
@@ -92,14 +101,18 @@ attention_rows_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
         }
         float sc = -CUDART_INF_F;
         if (valid) {
-            const T* kp = cache + ((size_t)page * 2 * KH + kh) * head_plane + (size_t)(key % P) * d;
+            const T* kp = cache + (size_t)page * page_elems + (size_t)kh * key_plane + (size_t)(key % P) * d;
             float acc = 0.f;
+            if (wide) {
 #pragma unroll 4
-            for (int c = 0; c < d; c += Vec<T>::N) {      // (unrolled: the next pieces are on their way while this one is added)
-                float kv[Vec<T>::N];
-                Vec<T>::load(kp + c, kv);
+                for (int c = 0; c < d; c += Vec<T>::N) {      // (unrolled: the next pieces are on their way while this one is added)
+                    float kv[Vec<T>::N];
+                    Vec<T>::load(kp + c, kv);
 #pragma unroll
-                for (int i = 0; i < Vec<T>::N; ++i) acc = fmaf(qs[c + i], kv[i], acc);
+                    for (int i = 0; i < Vec<T>::N; ++i) acc = fmaf(qs[c + i], kv[i], acc);
+                }
+            } else {
+                for (int c = 0; c < d; ++c) acc = fmaf(qs[c], dd_to_f32(kp[c]), acc);
             }
             sc = acc;
         }
@@ -122,11 +135,12 @@ attention_rows_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
                 const int j = min(j0 + u, n_valid - 1);     // past the last key: its row again, never added
                 pj[u] = __shfl_sync(0xffffffffu, p, j);
                 const int pg = __shfl_sync(0xffffffffu, page, j);
-                const T* vp = cache + ((size_t)pg * 2 * KH + KH + kh) * head_plane + (size_t)((base + j) % P) * d;
+                const T* vp = cache + (size_t)pg * page_elems + (size_t)KH * key_plane + (size_t)kh * value_plane +
+                              (size_t)((base + j) % P) * dv;
 #pragma unroll
                 for (int i = 0; i < DPL; ++i) {
                     const int c = lane + 32 * i;
-                    vv[u][i] = c < d ? dd_to_f32(vp[c]) : 0.f;
+                    vv[u][i] = c < dv ? dd_to_f32(vp[c]) : 0.f;
                 }
             }
 #pragma unroll
@@ -138,19 +152,20 @@ attention_rows_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
         }
     }
     if (n_splits == 1) {
-        const float inv = l > 0.f ? 1.0f / l : 0.f;
-        T* op = out + (size_t)t * out_stride + (size_t)h * d;
+        float inv = l > 0.f ? 1.0f / l : 0.f;
+        if (gate) inv *= 1.0f / (1.0f + expf(-dd_to_f32(gate[(size_t)t * gate_stride + h])));
+        T* op = out + (size_t)t * out_stride + (size_t)h * dv;
 #pragma unroll
         for (int i = 0; i < DPL; ++i) {
             const int c = lane + 32 * i;
-            if (c < d) op[c] = dd_from_f32<T>(o[i] * inv);
+            if (c < dv) op[c] = dd_from_f32<T>(o[i] * inv);
         }
     } else {
-        float* po = part_o + (size_t)item * d;
+        float* po = part_o + (size_t)item * dv;
 #pragma unroll
         for (int i = 0; i < DPL; ++i) {
             const int c = lane + 32 * i;
-            if (c < d) po[c] = o[i];
+            if (c < dv) po[c] = o[i];
         }
         if (lane == 0) {
             part_ml[2 * item] = m;
@@ -162,7 +177,8 @@ attention_rows_kernel(const T* __restrict__ q, int q_stride, const T* __restrict
 template <typename T>
 __global__ void __launch_bounds__(WARPS * 32)
 attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                       T* __restrict__ out, int out_stride, int n_tokens, int H, int d, int n_splits) {
+                       T* __restrict__ out, int out_stride, int n_tokens, int H, int d, int n_splits,
+                       const T* __restrict__ gate, int gate_stride) {
     dd_launch_dependents();
     dd_grid_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -171,6 +187,7 @@ attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict
     const float* ml = part_ml + (size_t)row * n_splits * 2;
     const int t = (int)(row / H), h = (int)(row % H);
     T* op = out + (size_t)t * out_stride + (size_t)h * d;
+    const float gated = gate ? 1.0f / (1.0f + expf(-dd_to_f32(gate[(size_t)t * gate_stride + h]))) : 1.0f;
     if (n_splits <= 32) {
         // Lane s fetches split s's maximum and sum; the merge then runs over the splits in order with values passed
         // between lanes, and the partial outputs of eight splits are requested together: the same additions in the same
@@ -185,7 +202,7 @@ attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict
             const float ls = __shfl_sync(0xffffffffu, my_l, s), ws = __shfl_sync(0xffffffffu, my_w, s);
             if (ls > 0.f) l += ls * ws;
         }
-        const float inv = l > 0.f ? 1.0f / l : 0.f;
+        const float inv = (l > 0.f ? 1.0f / l : 0.f) * gated;
         for (int c0 = 0; c0 < d; c0 += 32) {
             const int c = c0 + lane;
             float acc = 0.f;
@@ -210,7 +227,7 @@ attention_merge_kernel(const float* __restrict__ part_o, const float* __restrict
     float l = 0.f;
     for (int s = 0; s < n_splits; ++s)
         if (ml[2 * s + 1] > 0.f) l += ml[2 * s + 1] * expf(ml[2 * s] - m);
-    const float inv = l > 0.f ? 1.0f / l : 0.f;
+    const float inv = (l > 0.f ? 1.0f / l : 0.f) * gated;
     for (int c = lane; c < d; c += 32) {
         float acc = 0.f;
         for (int s = 0; s < n_splits; ++s)
@@ -223,7 +240,7 @@ template <typename T>
 int launch_rows(const void* q, int q_stride, const void* cache, const int* tok_entry, const int* tok_pos,
                 const int* block_table, int max_blocks, void* out, int out_stride, float* part_o, float* part_ml,
                 int n_tokens, int H, int KH, int d, int P, int n_pages, int window, float scale, int n_splits,
-                int* error_flag, cudaStream_t s) {
+                int* error_flag, cudaStream_t s, int dv, int chunk, const void* gate, int gate_stride) {
     const long long items = (long long)n_tokens * H * n_splits;
     if ((items + WARPS - 1) / WARPS > 0x7fffffffLL)
         return dd_fail("dd_attention_rows: %d tokens x %d heads x %d splits are more work items than one launch takes",
@@ -233,16 +250,16 @@ int launch_rows(const void* q, int q_stride, const void* cache, const int* tok_e
 #define DD_ROWS(DPL)                                                                                        \
     dd_launch(attention_rows_kernel<T, DPL>, dim3(grid), dim3(WARPS * 32), smem, s, (const T*)q, q_stride, (const T*)cache,    \
         tok_entry, tok_pos, block_table, max_blocks, (T*)out, out_stride, part_o, part_ml, n_tokens, H, KH, \
-        d, P, n_pages, window, scale, n_splits, error_flag)
-    if (d <= 32) DD_ROWS(1);
-    else if (d <= 64) DD_ROWS(2);
-    else if (d <= 128) DD_ROWS(4);
+        d, P, n_pages, window, scale, n_splits, error_flag, dv, chunk, (const T*)gate, gate_stride)
+    if (dv <= 32) DD_ROWS(1);
+    else if (dv <= 64) DD_ROWS(2);
+    else if (dv <= 128) DD_ROWS(4);
     else DD_ROWS(8);
 #undef DD_ROWS
     if (int e = dd_check_launch("dd_attention_rows")) return e;
     if (n_splits > 1) {
         dd_launch(attention_merge_kernel<T>, dim3(dd_ceil_div((long long)n_tokens * H, WARPS)), dim3(WARPS * 32), 0, s, 
-            part_o, part_ml, (T*)out, out_stride, n_tokens, H, d, n_splits);
+            part_o, part_ml, (T*)out, out_stride, n_tokens, H, dv, n_splits, (const T*)gate, gate_stride);
         return dd_check_launch("dd_attention_merge");
     }
     return 0;
@@ -253,29 +270,45 @@ int launch_rows(const void* q, int q_stride, const void* cache, const int* tok_e
 // part_o: float32 [n_tokens*H*n_splits*head_dim], part_ml: float32 [n_tokens*H*n_splits*2]
 // (scratch, used only when n_splits > 1). error_flag bit 2 (value 4): a page index
 // outside the pool was met and skipped.
+//
+// dd_attention_rows_masked takes four more: v_dim, the size of a value head (head_dim where keys and values have one
+// size; out then has heads of v_dim and the scratch v_dim floats per item); chunk, the chunk size of the mask (0: none);
+// gate and gate_stride, row views like q with one element per head (null: no gate).
+DD_API int dd_attention_rows_masked(const void* q, int q_stride, const void* cache, const int* tok_entry,
+                             const int* tok_pos, const int* block_table, int max_blocks, void* out, int out_stride,
+                             float* part_o, float* part_ml, int n_tokens, int n_heads, int n_kv_heads,
+                             int head_dim, int page_size, int n_pages, int window, float scale, int n_splits,
+                             int dtype, int* error_flag, void* stream, int v_dim, int chunk, const void* gate,
+                             int gate_stride) {
+    if (n_tokens <= 0) return 0;
+    if (head_dim <= 0 || head_dim > 256 || v_dim <= 0 || v_dim > 256)
+        return dd_fail("dd_attention_rows: head sizes %d and %d are not supported (at most 256)", head_dim, v_dim);
+    if (window < 0 || chunk < 0) return dd_fail("dd_attention_rows: window %d and chunk %d must not be negative", window, chunk);
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads)
+        return dd_fail("dd_attention_rows: %d heads cannot share %d key/value heads", n_heads, n_kv_heads);
+    if (n_splits < 1 || (n_splits > 1 && (!part_o || !part_ml)))
+        return dd_fail("dd_attention_rows: n_splits=%d needs scratch", n_splits);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == DD_F32)
+        return launch_rows<float>(q, q_stride, cache, tok_entry, tok_pos, block_table, max_blocks, out, out_stride,
+                                  part_o, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, page_size, n_pages,
+                                  window, scale, n_splits, error_flag, s, v_dim, chunk, gate, gate_stride);
+    if (dtype == DD_BF16)
+        return launch_rows<__nv_bfloat16>(q, q_stride, cache, tok_entry, tok_pos, block_table, max_blocks, out,
+                                          out_stride, part_o, part_ml, n_tokens, n_heads, n_kv_heads, head_dim,
+                                          page_size, n_pages, window, scale, n_splits, error_flag, s, v_dim, chunk, gate,
+                                          gate_stride);
+    return dd_fail("dd_attention_rows: unknown dtype %d", dtype);
+}
+
 DD_API int dd_attention_rows(const void* q, int q_stride, const void* cache, const int* tok_entry,
                              const int* tok_pos, const int* block_table, int max_blocks, void* out, int out_stride,
                              float* part_o, float* part_ml, int n_tokens, int n_heads, int n_kv_heads,
                              int head_dim, int page_size, int n_pages, int window, float scale, int n_splits,
                              int dtype, int* error_flag, void* stream) {
-    if (n_tokens <= 0) return 0;
-    if (head_dim <= 0 || head_dim > 256 || head_dim % 8)
-        return dd_fail("dd_attention_rows: head size %d is not supported (a multiple of 8, at most 256)", head_dim);
-    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads)
-        return dd_fail("dd_attention_rows: %d heads cannot share %d key/value heads", n_heads, n_kv_heads);
-    if (n_splits < 1 || (n_splits > 1 && (!part_o || !part_ml)))
-        return dd_fail("dd_attention_rows: n_splits=%d needs scratch", n_splits);
-    if (q_stride % 8 || out_stride % 8) return dd_fail("dd_attention_rows: row strides must be multiples of 8");
-    cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == DD_F32)
-        return launch_rows<float>(q, q_stride, cache, tok_entry, tok_pos, block_table, max_blocks, out, out_stride,
-                                  part_o, part_ml, n_tokens, n_heads, n_kv_heads, head_dim, page_size, n_pages,
-                                  window, scale, n_splits, error_flag, s);
-    if (dtype == DD_BF16)
-        return launch_rows<__nv_bfloat16>(q, q_stride, cache, tok_entry, tok_pos, block_table, max_blocks, out,
-                                          out_stride, part_o, part_ml, n_tokens, n_heads, n_kv_heads, head_dim,
-                                          page_size, n_pages, window, scale, n_splits, error_flag, s);
-    return dd_fail("dd_attention_rows: unknown dtype %d", dtype);
+    return dd_attention_rows_masked(q, q_stride, cache, tok_entry, tok_pos, block_table, max_blocks, out, out_stride, part_o,
+                                    part_ml, n_tokens, n_heads, n_kv_heads, head_dim, page_size, n_pages, window, scale,
+                                    n_splits, dtype, error_flag, stream, head_dim, 0, nullptr, 0);
 }
 
 // ---------------------------------------------------------------------------------------------

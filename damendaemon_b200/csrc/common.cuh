@@ -9,7 +9,7 @@
 #define DD_API extern "C" __attribute__((visibility("default")))
 
 enum DdDtype { DD_F32 = 0, DD_BF16 = 1 };
-enum DdAct { DD_ACT_NONE = 0, DD_ACT_GELU_NEW = 1, DD_ACT_GELU_ERF = 2 };
+enum DdAct { DD_ACT_NONE = 0, DD_ACT_GELU_NEW = 1, DD_ACT_GELU_ERF = 2, DD_ACT_RELU2 = 3 };
 
 // Records a message for dd_last_error() and returns a non-zero code.
 int dd_fail(const char* fmt, ...);
@@ -37,13 +37,15 @@ __device__ __forceinline__ float dd_warp_max(float v) {
     return v;
 }
 
-// gelu_new(u) = 0.5 u (1 + tanh(sqrt(2/pi) (u + 0.044715 u^3))); gelu(u) = 0.5 u (1 + erf(u / sqrt 2)).
+// gelu_new(u) = 0.5 u (1 + tanh(sqrt(2/pi) (u + 0.044715 u^3))); gelu(u) = 0.5 u (1 + erf(u / sqrt 2));
+// relu2(u) = max(u, 0)^2.
 __device__ __forceinline__ float dd_activation(float u, int act) {
     if (act == DD_ACT_GELU_NEW) {
         const float c = 0.7978845608028654f;
         return 0.5f * u * (1.0f + tanhf(c * (u + 0.044715f * u * u * u)));
     }
     if (act == DD_ACT_GELU_ERF) return 0.5f * u * (1.0f + erff(u * 0.7071067811865476f));
+    if (act == DD_ACT_RELU2) { const float r = fmaxf(u, 0.f); return r * r; }
     return u;
 }
 

@@ -13,11 +13,19 @@ template <typename TI, typename TO>
 __global__ void __launch_bounds__(THREADS)
 gemm_simt_kernel(const TI* __restrict__ A, int lda, const TI* __restrict__ W, int ldw,
                  const float* __restrict__ bias, const float* residual, int ldr,
-                 TO* C, int ldc, int M, int N, int K, int act) {
+                 TO* C, int ldc, int M, int N, int K, int act,
+                 const int* __restrict__ tile_group, long long group_stride) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     dd_launch_dependents();
     dd_grid_wait();
+    if (tile_group) {
+        // grouped product: the BM rows of this tile all belong to one group, whose own W (one of a stack of equal
+        // matrices, group_stride elements apart) they are multiplied with; a tile without a group has no rows
+        const int g = tile_group[blockIdx.y];
+        if (g < 0) return;
+        W += (size_t)g * group_stride;
+    }
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     const int lr = threadIdx.x >> 2, lk = (threadIdx.x & 3) * 4;
@@ -267,10 +275,42 @@ int launch(const void* A, int lda, const void* W, int ldw, const float* bias, co
     dim3 grid(dd_ceil_div(N, BN), dd_ceil_div(M, BM));
     if (grid.y > 65535) return dd_fail("dd_gemm_simt: too many rows (%d)", M);
     dd_launch(gemm_simt_kernel<TI, TO>, dim3(grid), dim3(THREADS), 0, s, (const TI*)A, lda, (const TI*)W, ldw, bias, residual, ldr,
-                                                     (TO*)C, ldc, M, N, K, act);
+                                                     (TO*)C, ldc, M, N, K, act, (const int*)nullptr, 0LL);
     return dd_check_launch("dd_gemm_simt");
 }
+
+template <typename TI, typename TO>
+int launch_grouped(const void* A, int lda, const void* W, int ldw, long long group_stride, const int* tile_group,
+                   void* C, int ldc, int M, int N, int K, int act, cudaStream_t s) {
+    dim3 grid(dd_ceil_div(N, BN), dd_ceil_div(M, BM));
+    if (grid.y > 65535) return dd_fail("dd_gemm_simt_grouped: too many rows (%d)", M);
+    dd_launch(gemm_simt_kernel<TI, TO>, dim3(grid), dim3(THREADS), 0, s, (const TI*)A, lda, (const TI*)W, ldw,
+              (const float*)nullptr, (const float*)nullptr, 0, (TO*)C, ldc, M, N, K, act, tile_group, group_stride);
+    return dd_check_launch("dd_gemm_simt_grouped");
+}
 }  // namespace
+
+// Rows of A per tile of the grouped product: a group's rows start on a multiple of it.
+DD_API int dd_gemm_simt_group_tile() { return BM; }
+
+// Grouped product: W is a stack of matrices [groups][N, K] (group_stride elements apart, rows ldw apart); the rows
+// of A come in tiles of dd_gemm_simt_group_tile() rows, tile i multiplied with matrix tile_group[i] (a device array
+// of ceil(M / tile) entries; -1: the tile holds no rows and is skipped, its rows of C are left as they are).
+// The arithmetic per output element is that of dd_gemm_simt (k ascending, fmaf from zero).
+DD_API int dd_gemm_simt_grouped(const void* A, int lda, const void* W, int ldw, long long group_stride,
+                                const int* tile_group, void* C, int ldc, int M, int N, int K, int act,
+                                int in_dtype, int out_dtype, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || !tile_group) return dd_fail("dd_gemm_simt_grouped: bad K=%d or no tile groups", K);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (in_dtype == DD_F32 && out_dtype == DD_F32)
+        return launch_grouped<float, float>(A, lda, W, ldw, group_stride, tile_group, C, ldc, M, N, K, act, s);
+    if (in_dtype == DD_BF16 && out_dtype == DD_F32)
+        return launch_grouped<__nv_bfloat16, float>(A, lda, W, ldw, group_stride, tile_group, C, ldc, M, N, K, act, s);
+    if (in_dtype == DD_BF16 && out_dtype == DD_BF16)
+        return launch_grouped<__nv_bfloat16, __nv_bfloat16>(A, lda, W, ldw, group_stride, tile_group, C, ldc, M, N, K, act, s);
+    return dd_fail("dd_gemm_simt_grouped: unsupported dtypes in=%d out=%d", in_dtype, out_dtype);
+}
 
 // A [M,K] (row stride lda) and W [N,K] (row stride ldw) in in_dtype; bias [N] and
 // residual [M,N] (row stride ldr, may be the output itself) float32 or null.

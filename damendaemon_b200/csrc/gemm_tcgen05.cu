@@ -133,6 +133,7 @@ __device__ __forceinline__ void store16(const GemmParams& p, int m_first, int n,
                 v = 0.5f * v * (1.0f + t);
             } else v = dd_activation(v, DD_ACT_GELU_NEW);
         } else if (ACT == DD_ACT_GELU_ERF) v = dd_activation(v, DD_ACT_GELU_ERF);
+        else if (ACT == DD_ACT_RELU2) v = dd_activation(v, DD_ACT_RELU2);
         if (RESIDUAL) v += r[j];
         if (BF16_OUT) reinterpret_cast<__nv_bfloat16*>(p.out)[(size_t)(m_first + j) * p.ldo + n] = __float2bfloat16_rn(v);
         else reinterpret_cast<float*>(p.out)[(size_t)(m_first + j) * p.ldo + n] = v;
@@ -162,6 +163,7 @@ __device__ __forceinline__ void load_residual16(const GemmParams& p, int m_first
 __device__ __forceinline__ void store_out16(const GemmParams& p, int m_first, int n, const float* acc, const float* r, float b) {
     if (p.act == DD_ACT_NONE) store16_o<DD_ACT_NONE>(p, m_first, n, acc, b, r);
     else if (p.act == DD_ACT_GELU_NEW) store16_o<DD_ACT_GELU_NEW>(p, m_first, n, acc, b, r);
+    else if (p.act == DD_ACT_RELU2) store16_o<DD_ACT_RELU2>(p, m_first, n, acc, b, r);
     else store16_o<DD_ACT_GELU_ERF>(p, m_first, n, acc, b, r);
 }
 
@@ -223,6 +225,7 @@ __device__ __forceinline__ void store_row16(const GemmParams& p, int m, int n_fi
                 u = 0.5f * u * (1.0f + t);
             } else u = dd_activation(u, DD_ACT_GELU_NEW);
         } else if (ACT == DD_ACT_GELU_ERF) u = dd_activation(u, DD_ACT_GELU_ERF);
+        else if (ACT == DD_ACT_RELU2) u = dd_activation(u, DD_ACT_RELU2);
         if (RESIDUAL) u += r[j];
         v[j] = u;
     }
@@ -274,6 +277,7 @@ __device__ __forceinline__ void store_row16_o(const GemmParams& p, int m, int n_
 __device__ __forceinline__ void store_out_row16(const GemmParams& p, int m, int n_first, const uint32_t* acc, const float* r, float* v) {
     if (p.act == DD_ACT_NONE) store_row16_o<DD_ACT_NONE>(p, m, n_first, acc, r, v);
     else if (p.act == DD_ACT_GELU_NEW) store_row16_o<DD_ACT_GELU_NEW>(p, m, n_first, acc, r, v);
+    else if (p.act == DD_ACT_RELU2) store_row16_o<DD_ACT_RELU2>(p, m, n_first, acc, r, v);
     else store_row16_o<DD_ACT_GELU_ERF>(p, m, n_first, acc, r, v);
 }
 

@@ -1,5 +1,7 @@
 // Write this step's keys and values into the request's cache pages.
-// Cache layout of one layer: [n_pages, 2 (K, V), kv_heads, page_size, head_dim].
+// Cache layout of one layer: [n_pages, 2 (K, V), kv_heads, page_size, head_dim]; when a value head has another
+// size than a key head, a page is its key plane [kv_heads, page_size, head_dim] followed by its value plane
+// [kv_heads, page_size, v_dim].
 // The page of a token is block_table[entry][position / page_size]
 // (the reference stores with index assignment, damendaemon/gpt2.py:50-51, and
 // through a page table in damendaemon/kernels.py:270-340).
@@ -10,7 +12,7 @@ __global__ void kv_store_kernel(const T* __restrict__ k_src, const T* __restrict
                                 const int* __restrict__ tok_entry, const int* __restrict__ tok_pos,
                                 const int* __restrict__ block_table, int max_blocks,
                                 T* __restrict__ cache, int n_pages, int kv_heads, int page_size, int head_dim,
-                                int* __restrict__ error_flag) {
+                                int v_dim, int* __restrict__ error_flag) {
     dd_launch_dependents();
     // positions, entries and the block table are the step's inputs: the page is known before the projection has finished
     const int t = blockIdx.x;
@@ -23,12 +25,23 @@ __global__ void kv_store_kernel(const T* __restrict__ k_src, const T* __restrict
         return;
     }
     const int row = kv_heads * head_dim;
-    const size_t plane = (size_t)kv_heads * page_size * head_dim;
-    T* k_dst = cache + (size_t)page * 2 * plane + (size_t)(pos % page_size) * head_dim;
-    T* v_dst = k_dst + plane;
+    const size_t plane = (size_t)kv_heads * page_size * head_dim, v_plane = (size_t)kv_heads * page_size * v_dim;
+    T* k_dst = cache + (size_t)page * (plane + v_plane) + (size_t)(pos % page_size) * head_dim;
+    T* v_dst = cache + (size_t)page * (plane + v_plane) + plane + (size_t)(pos % page_size) * v_dim;
     const T* ks = k_src + (size_t)t * src_stride;
     const T* vs = v_src + (size_t)t * src_stride;
     constexpr int V = 16 / sizeof(T);       // elements per 16-byte copy
+    if (v_dim != head_dim) {
+        for (int c = threadIdx.x; c < row; c += blockDim.x) {
+            const int h = c / head_dim, i = c - h * head_dim;
+            k_dst[(size_t)h * page_size * head_dim + i] = ks[c];
+        }
+        for (int c = threadIdx.x; c < kv_heads * v_dim; c += blockDim.x) {
+            const int h = c / v_dim, i = c - h * v_dim;
+            v_dst[(size_t)h * page_size * v_dim + i] = vs[c];
+        }
+        return;
+    }
     if (head_dim % V == 0 && src_stride % V == 0 && (((uintptr_t)k_src | (uintptr_t)v_src | (uintptr_t)cache) & 15) == 0) {
         for (int c = threadIdx.x * V; c < row; c += blockDim.x * V) {
             const int h = c / head_dim, i = c - h * head_dim;
@@ -46,21 +59,22 @@ __global__ void kv_store_kernel(const T* __restrict__ k_src, const T* __restrict
     }
 }
 
-// k_src/v_src: first key / value element of token 0; rows are src_stride elements apart.
+// k_src/v_src: first key / value element of token 0; rows are src_stride elements apart. v_dim: size of a value
+// head (head_dim where keys and values have one size).
 DD_API int dd_kv_store(const void* k_src, const void* v_src, int src_stride, const int* tok_entry,
                        const int* tok_pos, const int* block_table, int max_blocks, void* cache, int n_pages,
-                       int kv_heads, int page_size, int head_dim, int n_tokens, int dtype, int* error_flag,
+                       int kv_heads, int page_size, int head_dim, int v_dim, int n_tokens, int dtype, int* error_flag,
                        void* stream) {
     if (n_tokens <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int threads = kv_heads * head_dim >= 1024 ? 256 : 128;
     if (dtype == DD_F32)
         dd_launch(kv_store_kernel<float>, dim3(n_tokens), dim3(threads), 0, s, (const float*)k_src, (const float*)v_src, src_stride,
-            tok_entry, tok_pos, block_table, max_blocks, (float*)cache, n_pages, kv_heads, page_size, head_dim, error_flag);
+            tok_entry, tok_pos, block_table, max_blocks, (float*)cache, n_pages, kv_heads, page_size, head_dim, v_dim, error_flag);
     else if (dtype == DD_BF16)
         dd_launch(kv_store_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, s, (const __nv_bfloat16*)k_src, (const __nv_bfloat16*)v_src,
             src_stride, tok_entry, tok_pos, block_table, max_blocks, (__nv_bfloat16*)cache, n_pages, kv_heads, page_size,
-            head_dim, error_flag);
+            head_dim, v_dim, error_flag);
     else
         return dd_fail("dd_kv_store: unknown dtype %d", dtype);
     return dd_check_launch("dd_kv_store");

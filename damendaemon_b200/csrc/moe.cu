@@ -1,0 +1,168 @@
+// Experts chosen per token by a table: the bookkeeping around the grouped products.
+//
+// A token uses K of E experts. The (token, choice) pairs are laid out expert by expert in a buffer of rows in
+// which every expert's rows start on a multiple of the product's row tile, so that a tile of rows meets one
+// expert's matrices only (tile_group[tile] = that expert, or -1 for a tile no pair fell into):
+//
+//   dd_route_by_table   token ids + table [vocab, K] -> pair_row [N*K] (the row of pair (t, k)), row_token [rows]
+//                       (the token of a row, -1 for a row of padding), tile_group [rows / tile]
+//   dd_gather_rows      x [N, width] -> sorted rows (a row of padding is zeroed)
+//   dd_gated_unit       rows of [gate | up] halves -> g = min(gate, limit), u = clamp(up, -limit, limit),
+//                       y = g * sigmoid(alpha g) * (u + 1), in float32
+//   dd_combine_rows     stream[t] += sum over k of weight * y[pair_row[t*K + k]], k ascending, in float32
+//
+// The order of an expert's rows among themselves depends on the order in which threads arrive; no value depends
+// on it, since every row is computed by itself and the sum over a token's experts runs in the order of its choices.
+#include "common.cuh"
+
+namespace {
+constexpr int ROUTE_THREADS = 1024;
+
+__global__ void __launch_bounds__(ROUTE_THREADS)
+route_by_table_kernel(const int* __restrict__ ids, const int* __restrict__ table, int n_tokens, int vocab, int top,
+                      int n_experts, int tile, int n_rows, int* __restrict__ pair_row, int* __restrict__ row_token,
+                      int* __restrict__ tile_group, int* __restrict__ error_flag) {
+    extern __shared__ int shared[];              // [E] counts, then cursors; [E + 1] first rows
+    int* count = shared;
+    int* first = shared + n_experts;
+    dd_launch_dependents();
+    dd_grid_wait();
+    const int n_pairs = n_tokens * top;
+    for (int e = threadIdx.x; e < n_experts; e += ROUTE_THREADS) count[e] = 0;
+    for (int r = threadIdx.x; r < n_rows; r += ROUTE_THREADS) row_token[r] = -1;
+    for (int i = threadIdx.x; i < n_rows / tile; i += ROUTE_THREADS) tile_group[i] = -1;
+    __syncthreads();
+    for (int pair = threadIdx.x; pair < n_pairs; pair += ROUTE_THREADS) {
+        const int id = ids[pair / top];
+        const int e = (id >= 0 && id < vocab) ? table[(size_t)id * top + pair % top] : -1;
+        if (e < 0 || e >= n_experts) atomicOr(error_flag, 1);
+        else atomicAdd(&count[e], 1);
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int row = 0;
+        for (int e = 0; e < n_experts; ++e) {
+            first[e] = row;
+            const int tiles = (count[e] + tile - 1) / tile;
+            for (int i = 0; i < tiles; ++i) tile_group[row / tile + i] = e;
+            row += tiles * tile;
+            count[e] = 0;                        // from here on: the expert's cursor
+        }
+        first[n_experts] = row;
+    }
+    __syncthreads();
+    for (int pair = threadIdx.x; pair < n_pairs; pair += ROUTE_THREADS) {
+        const int id = ids[pair / top];
+        const int e = (id >= 0 && id < vocab) ? table[(size_t)id * top + pair % top] : -1;
+        if (e < 0 || e >= n_experts) {
+            pair_row[pair] = -1;
+            continue;
+        }
+        const int row = first[e] + atomicAdd(&count[e], 1);
+        pair_row[pair] = row;
+        row_token[row] = pair / top;
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ row_token, T* __restrict__ out, int width) {
+    dd_launch_dependents();
+    dd_grid_wait();
+    const int row = blockIdx.x;
+    const int t = row_token[row];
+    T* o = out + (size_t)row * width;
+    constexpr int V = 16 / sizeof(T);
+    if (width % V == 0 && !(((uintptr_t)x | (uintptr_t)out) & 15)) {
+        const uint4* src = t >= 0 ? reinterpret_cast<const uint4*>(x + (size_t)t * width) : nullptr;
+        for (int c = threadIdx.x; c < width / V; c += blockDim.x)
+            reinterpret_cast<uint4*>(o)[c] = src ? src[c] : make_uint4(0u, 0u, 0u, 0u);
+        return;
+    }
+    for (int c = threadIdx.x; c < width; c += blockDim.x) o[c] = t >= 0 ? x[(size_t)t * width + c] : dd_from_f32<T>(0.f);
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+gated_unit_kernel(const T* __restrict__ gate_up, int stride, T* __restrict__ out, int out_stride, int rows, int inner,
+                  float limit, float alpha) {
+    dd_launch_dependents();
+    dd_grid_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= (long long)rows * inner) return;
+    const int row = (int)(i / inner), c = (int)(i - (long long)row * inner);
+    const float g = fminf(dd_to_f32(gate_up[(size_t)row * stride + c]), limit);
+    const float u = fminf(fmaxf(dd_to_f32(gate_up[(size_t)row * stride + inner + c]), -limit), limit);
+    out[(size_t)row * out_stride + c] = dd_from_f32<T>(g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f));
+}
+
+__global__ void __launch_bounds__(128)
+combine_rows_kernel(const float* __restrict__ y, const int* __restrict__ pair_row, float* __restrict__ stream, int width,
+                    int top, float weight) {
+    dd_launch_dependents();
+    dd_grid_wait();
+    const int t = blockIdx.x;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) {
+            const int row = pair_row[(size_t)t * top + k];
+            if (row >= 0) sum += y[(size_t)row * width + c];
+        }
+        stream[(size_t)t * width + c] += sum * weight;
+    }
+}
+}  // namespace
+
+// n_rows: rows of the sorted buffer, a multiple of tile and at least n_tokens * top + min(n_experts, n_tokens * top)
+// * (tile - 1): every expert that has a pair may waste all but one row of its last tile. A token id or a table entry out of range sets error bit 1 and leaves its pair out.
+DD_API int dd_route_by_table(const int* ids, const int* table, int n_tokens, int vocab, int top, int n_experts, int tile,
+                             int n_rows, int* pair_row, int* row_token, int* tile_group, int* error_flag, void* stream) {
+    if (n_tokens <= 0) return 0;
+    const long long n_pairs = (long long)n_tokens * top;
+    if (top <= 0 || n_experts <= 0 || tile <= 0 || n_rows % tile ||
+        (long long)n_rows < n_pairs + (n_pairs < n_experts ? n_pairs : (long long)n_experts) * (tile - 1))
+        return dd_fail("dd_route_by_table: %d rows in tiles of %d do not hold %d tokens x %d of %d experts", n_rows, tile,
+                       n_tokens, top, n_experts);
+    if (n_experts > 8192) return dd_fail("dd_route_by_table: %d experts are more than a block counts", n_experts);
+    dd_launch(route_by_table_kernel, dim3(1), dim3(ROUTE_THREADS), (size_t)(2 * n_experts + 1) * sizeof(int), (cudaStream_t)stream,
+              ids, table, n_tokens, vocab, top, n_experts, tile, n_rows, pair_row, row_token, tile_group, error_flag);
+    return dd_check_launch("dd_route_by_table");
+}
+
+DD_API int dd_gather_rows(const void* x, const int* row_token, void* out, int n_rows, int width, int dtype, void* stream) {
+    if (n_rows <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == DD_F32)
+        dd_launch(gather_rows_kernel<float>, dim3(n_rows), dim3(128), 0, s, (const float*)x, row_token, (float*)out, width);
+    else if (dtype == DD_BF16)
+        dd_launch(gather_rows_kernel<__nv_bfloat16>, dim3(n_rows), dim3(128), 0, s, (const __nv_bfloat16*)x, row_token,
+                  (__nv_bfloat16*)out, width);
+    else
+        return dd_fail("dd_gather_rows: unknown dtype %d", dtype);
+    return dd_check_launch("dd_gather_rows");
+}
+
+// gate_up: rows of `stride` elements, the gate's `inner` values followed by the up projection's.
+DD_API int dd_gated_unit(const void* gate_up, int stride, void* out, int out_stride, int rows, int inner, float limit,
+                         float alpha, int dtype, void* stream) {
+    if (rows <= 0 || inner <= 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int grid = dd_ceil_div((long long)rows * inner, 256);
+    if (dtype == DD_F32)
+        dd_launch(gated_unit_kernel<float>, dim3(grid), dim3(256), 0, s, (const float*)gate_up, stride, (float*)out,
+                  out_stride, rows, inner, limit, alpha);
+    else if (dtype == DD_BF16)
+        dd_launch(gated_unit_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, (const __nv_bfloat16*)gate_up, stride,
+                  (__nv_bfloat16*)out, out_stride, rows, inner, limit, alpha);
+    else
+        return dd_fail("dd_gated_unit: unknown dtype %d", dtype);
+    return dd_check_launch("dd_gated_unit");
+}
+
+DD_API int dd_combine_rows(const float* y, const int* pair_row, float* stream_rows, int n_tokens, int width, int top,
+                           float weight, void* stream) {
+    if (n_tokens <= 0) return 0;
+    dd_launch(combine_rows_kernel, dim3(n_tokens), dim3(128), 0, (cudaStream_t)stream, y, pair_row, stream_rows, width, top,
+              weight);
+    return dd_check_launch("dd_combine_rows");
+}

@@ -1,0 +1,109 @@
+// RMS norm over the float32 residual stream: y = x / sqrt(mean(x^2) + eps) * (offset + w), eps inside the root,
+// the sum of squares and the scaling in float32. `offset` is 0 for a weight stored as the factor itself and 1 for a
+// weight stored as its distance from one. Output in the engine dtype. An optional row index gathers rows first (the
+// final norm runs only where logits are wanted).
+#include "common.cuh"
+
+namespace {
+template <int THREADS>
+__device__ __forceinline__ float rms_block_sum(float v, float* scratch) {
+    v = dd_warp_sum(v);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    float total = 0.f;
+#pragma unroll
+    for (int w = 0; w < THREADS / 32; ++w) total += scratch[w];
+    return total;
+}
+
+template <typename TO> struct RmsPack4;
+template <> struct RmsPack4<float> {
+    __device__ static void store(float* dst, float a, float b, float c, float d) { *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d); }
+};
+template <> struct RmsPack4<__nv_bfloat16> {
+    __device__ static void store(__nv_bfloat16* dst, float a, float b, float c, float d) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        uint2 v;
+        v.x = *reinterpret_cast<uint32_t*>(&lo);
+        v.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(dst) = v;
+    }
+};
+
+// Rows whose width is a multiple of 4 and at most 128 * 4 * VPT: the row in registers as float4.
+template <typename TO, int VPT>
+__global__ void __launch_bounds__(128)
+rmsnorm_vec_kernel(const float* __restrict__ x, const int* __restrict__ row_index, const float* __restrict__ weight,
+                   TO* __restrict__ out, int width, float eps, float offset) {
+    __shared__ float scratch[4];
+    dd_launch_dependents();
+    const int row = blockIdx.x;
+    const int n4 = width >> 2;
+    // the weight does not depend on the kernel before: it is in registers before that kernel has finished
+    float4 g[VPT];
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * 128;
+        g[i] = c < n4 ? __ldg(reinterpret_cast<const float4*>(weight) + c) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    dd_grid_wait();
+    const float4* in = reinterpret_cast<const float4*>(x + (size_t)(row_index ? row_index[row] : row) * width);
+    float4 v[VPT];
+    float sq = 0.f;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * 128;
+        v[i] = c < n4 ? in[c] : make_float4(0.f, 0.f, 0.f, 0.f);
+        sq += (v[i].x * v[i].x + v[i].y * v[i].y) + (v[i].z * v[i].z + v[i].w * v[i].w);
+    }
+    const float r = 1.0f / sqrtf(rms_block_sum<128>(sq, scratch) / (float)width + eps);
+    TO* o = out + (size_t)row * width;
+#pragma unroll
+    for (int i = 0; i < VPT; ++i) {
+        const int c = threadIdx.x + i * 128;
+        if (c < n4)
+            RmsPack4<TO>::store(o + 4 * c, v[i].x * r * (offset + g[i].x), v[i].y * r * (offset + g[i].y),
+                                v[i].z * r * (offset + g[i].z), v[i].w * r * (offset + g[i].w));
+    }
+}
+
+template <typename TO, int THREADS>
+__global__ void __launch_bounds__(THREADS)
+rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ row_index, const float* __restrict__ weight,
+               TO* __restrict__ out, int width, float eps, float offset) {
+    __shared__ float scratch[THREADS / 32];
+    dd_launch_dependents();
+    dd_grid_wait();
+    const int row = blockIdx.x;
+    const float* in = x + (size_t)(row_index ? row_index[row] : row) * width;
+    TO* o = out + (size_t)row * width;
+    float sq = 0.f;
+    for (int c = threadIdx.x; c < width; c += THREADS) sq += in[c] * in[c];
+    const float r = 1.0f / sqrtf(rms_block_sum<THREADS>(sq, scratch) / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += THREADS) o[c] = dd_from_f32<TO>(in[c] * r * (offset + weight[c]));
+}
+}  // namespace
+
+DD_API int dd_rmsnorm(const float* x, const int* row_index, const float* weight, void* out, int rows, int width,
+                      float eps, float offset, int out_dtype, void* stream) {
+    if (rows <= 0) return 0;
+    if (width <= 0) return dd_fail("dd_rmsnorm: bad width %d", width);
+    if (out_dtype != DD_F32 && out_dtype != DD_BF16) return dd_fail("dd_rmsnorm: unknown output dtype %d", out_dtype);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (width % 4 == 0 && width <= 128 * 4 * 4 && !(((uintptr_t)x | (uintptr_t)out | (uintptr_t)weight) & 15)) {
+        if (out_dtype == DD_F32)
+            dd_launch(rmsnorm_vec_kernel<float, 4>, dim3(rows), dim3(128), 0, s, x, row_index, weight, (float*)out, width, eps, offset);
+        else
+            dd_launch(rmsnorm_vec_kernel<__nv_bfloat16, 4>, dim3(rows), dim3(128), 0, s, x, row_index, weight,
+                      (__nv_bfloat16*)out, width, eps, offset);
+        return dd_check_launch("dd_rmsnorm");
+    }
+    if (out_dtype == DD_F32)
+        dd_launch(rmsnorm_kernel<float, 256>, dim3(rows), dim3(256), 0, s, x, row_index, weight, (float*)out, width, eps, offset);
+    else
+        dd_launch(rmsnorm_kernel<__nv_bfloat16, 256>, dim3(rows), dim3(256), 0, s, x, row_index, weight,
+                  (__nv_bfloat16*)out, width, eps, offset);
+    return dd_check_launch("dd_rmsnorm");
+}

@@ -51,9 +51,11 @@ def require_cuda(device):
 class Engine:
     def __init__(self, model_dir=None, *, config=None, tensors=None, dtype="bfloat16", kv_tokens=None,
                  page_size=16, max_requests=64, device="cuda:0", gemm="auto", check_device_errors=True,
-                 use_graph=False):
+                 use_graph=False, max_context=None):
         """Either ``model_dir`` (config.json + model.safetensors) or ``config`` (the raw
-        config.json dict) with ``tensors`` ({checkpoint name: tensor})."""
+        config.json dict) with ``tensors`` ({checkpoint name: tensor}). ``max_context``: most tokens a
+        request may hold, at most the model's positions; for an architecture that names no limit the
+        default is the cache's size in tokens, or ``UNBOUNDED_CONTEXT`` without one."""
         self.device = require_cuda(device)
         torch.cuda.set_device(self.device)
         self.dtype = DTYPES[dtype]
@@ -76,7 +78,10 @@ class Engine:
         self.model = DecoderModel(self.spec, weights, self.runtime)
         self.weight_bytes = sum(t.numel() * t.element_size() for t in weights.values())
         self.page_size = page_size
-        self.max_context = self.spec.max_positions
+        limit = self.spec.max_positions
+        if limit is None:
+            limit = max_context or kv_tokens or self.UNBOUNDED_CONTEXT
+        self.max_context = min(limit, max_context or limit)
         # where a scheduler should cut a prompt that it has to cut: where the model's mixers like it (a key block of a
         # prompt attention kernel), 1 if they do not care
         self.portion_multiple = self.model.portion_multiple
@@ -118,6 +123,7 @@ class Engine:
         self.tokens_run = 0
 
     HEADROOM_BYTES = 512 << 20
+    UNBOUNDED_CONTEXT = 8192        # tokens per request when neither the model nor the caller sets a limit
 
     def _admit_memory(self):
         """Weights are on the device already; the cache, the activations of the largest step and 512 MiB of

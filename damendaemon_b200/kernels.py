@@ -14,7 +14,7 @@ import torch
 from .csrc import build
 
 F32, BF16 = 0, 1
-ACTIVATIONS = {None: 0, "none": 0, "gelu_new": 1, "gelu": 2}
+ACTIVATIONS = {None: 0, "none": 0, "gelu_new": 1, "gelu": 2, "relu2": 3}
 
 _c_int, _c_float, _c_void = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 
@@ -27,12 +27,22 @@ _SIGNATURES = {
     "core": {
         "dd_device_arch": [],
         "dd_copy_to_device": [_c_void, _c_void, ctypes.c_longlong, _c_void],
-        "dd_embed": [_c_void] * 5 + [_c_int] * 5 + [_c_void, _c_void],
+        "dd_embed": [_c_void] * 5 + [_c_int] * 5 + [_c_float, _c_void, _c_void],
         "dd_layernorm": [_c_void] * 5 + [_c_int, _c_int, _c_float, _c_int, _c_void],
+        "dd_rmsnorm": [_c_void] * 4 + [_c_int, _c_int, _c_float, _c_float, _c_int, _c_void],
+        "dd_rotary": [_c_void, _c_void, _c_int, _c_void, _c_void, _c_float] + [_c_int] * 7 + [_c_void],
+        "dd_gemm_simt_group_tile": [],
+        "dd_gemm_simt_grouped": [_c_void, _c_int, _c_void, _c_int, ctypes.c_longlong, _c_void, _c_void, _c_int] + [_c_int] * 6 + [_c_void],
+        "dd_route_by_table": [_c_void, _c_void] + [_c_int] * 6 + [_c_void] * 5,
+        "dd_gather_rows": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void],
+        "dd_gated_unit": [_c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_void],
+        "dd_combine_rows": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_float, _c_void],
         "dd_gemm_simt": [_c_void, _c_int, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int] + [_c_int] * 6 + [_c_void],
-        "dd_kv_store": [_c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_void] + [_c_int] * 6 + [_c_void, _c_void],
+        "dd_kv_store": [_c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_void] + [_c_int] * 7 + [_c_void, _c_void],
         "dd_attention_rows": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int, _c_void, _c_void]
                              + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_void, _c_void],
+        "dd_attention_rows_masked": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int, _c_void, _c_void]
+                                    + [_c_int] * 7 + [_c_float, _c_int, _c_int, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int],
         "dd_sample": [_c_void, _c_int, _c_int, _c_int] + [_c_void] * 6,
         "dd_adjust_logits": [_c_void, _c_int, _c_int] + [_c_void] * 8 + [_c_int, _c_void],
     },
@@ -220,7 +230,8 @@ def wait_probe(limit_ns, device):
 
 # ---------------------------------------------------------------- kernels
 
-def embed(ids, positions, token_table, position_table=None, out=None):
+def embed(ids, positions, token_table, position_table=None, out=None, scale=1.0):
+    """x[t] = token_table[ids[t]] * scale (+ position_table[positions[t]]), float32."""
     n, width = ids.numel(), token_table.shape[1]
     if out is None:
         out = torch.empty((n, width), dtype=torch.float32, device=ids.device)
@@ -229,7 +240,7 @@ def embed(ids, positions, token_table, position_table=None, out=None):
     _call(library("core"), "dd_embed", _ptr(ids, "ids", torch.int32), _ptr(positions, "positions", torch.int32),
           _ptr(token_table, "token table"), _ptr(position_table, "position table"), _ptr(out, "out", torch.float32),
           n, width, token_table.shape[0], 0 if position_table is None else position_table.shape[0],
-          _dt(token_table.dtype), _ptr(error_flag(ids.device)), _stream())
+          _dt(token_table.dtype), float(scale), _ptr(error_flag(ids.device)), _stream())
     return out
 
 
@@ -245,6 +256,35 @@ def layernorm(x, gamma, beta, eps, out_dtype, row_index=None, out=None):
           _ptr(gamma, "gamma", torch.float32), _ptr(beta, "beta", torch.float32), _ptr(out, "out", out_dtype),
           rows, width, float(eps), _dt(out_dtype), _stream())
     return out
+
+
+def rmsnorm(x, weight, eps, out_dtype, row_index=None, offset=0.0, out=None):
+    """x / sqrt(mean(x^2) + eps) * (offset + weight) over float32 rows; offset 1 for a weight stored around zero."""
+    _rows(x, "x")
+    rows = x.shape[0] if row_index is None else row_index.numel()
+    width = x.shape[1]
+    if not x.is_contiguous():
+        raise KernelError("rmsnorm input must be contiguous")
+    if out is None:
+        out = torch.empty((rows, width), dtype=out_dtype, device=x.device)
+    _call(library("core"), "dd_rmsnorm", _ptr(x, "x", torch.float32), _ptr(row_index, "row_index", torch.int32),
+          _ptr(weight, "weight", torch.float32), _ptr(out, "out", out_dtype), rows, width, float(eps), float(offset),
+          _dt(out_dtype), _stream())
+    return out
+
+
+def rotary(q, k, positions, freqs, magnitude, q_heads, k_heads, head_dim, interleaved=True):
+    """Rotate, in place, the first 2 * len(freqs) dimensions of every head of q and k (row views of one buffer) by
+    position * freqs; cosine and sine are multiplied by magnitude. interleaved: pairs are neighbours (2i, 2i+1);
+    else the two halves of the rotated dimensions (i, i + len(freqs))."""
+    if q.stride(0) != k.stride(0) or q.stride(1) != 1 or k.stride(1) != 1 or q.dtype != k.dtype:
+        raise KernelError("rotary: q and k must be row views of one buffer")
+    if q.shape[1] != q_heads * head_dim or k.shape[1] != k_heads * head_dim or 2 * freqs.numel() > head_dim:
+        raise KernelError("rotary: shapes do not fit the heads")
+    _call(library("core"), "dd_rotary", _ptr(q, "q"), _ptr(k, "k"), q.stride(0), _ptr(positions, "positions", torch.int32),
+          _ptr(freqs, "freqs", torch.float32), float(magnitude), q.shape[0], q_heads, k_heads, head_dim, freqs.numel(),
+          1 if interleaved else 0, _dt(q.dtype), _stream())
+    return q, k
 
 
 def gemm_simt(a, w, bias=None, residual=None, activation=None, out_dtype=None, out=None):
@@ -267,39 +307,129 @@ def gemm_simt(a, w, bias=None, residual=None, activation=None, out_dtype=None, o
     return out
 
 
-def kv_store(k, v, token_entry, positions, block_table, cache, n_tokens=None):
-    """k, v: [N, kv_heads*head_dim] views (row stride free); cache [pages, 2, kv_heads, page, head_dim]."""
-    n_pages, _, kv_heads, page_size, head_dim = cache.shape
+def cache_geometry(cache, kv_heads=None, head_dim=None, v_dim=None):
+    """(pages, kv_heads, page_size, head_dim, v_dim) of a layer's cache: [pages, 2, kv_heads, page, head_dim], or, where
+    a value head has another size than a key head, [pages, kv_heads * page * (head_dim + v_dim)] (a page's key plane
+    followed by its value plane), whose sizes the caller names."""
+    if cache.dim() == 5:
+        return cache.shape[0], cache.shape[2], cache.shape[3], cache.shape[4], cache.shape[4]
+    if cache.dim() != 2 or not kv_heads or not head_dim or not v_dim or cache.shape[1] % (kv_heads * (head_dim + v_dim)):
+        raise KernelError(f"a cache of shape {tuple(cache.shape)} needs its head count and head sizes named")
+    return cache.shape[0], kv_heads, cache.shape[1] // (kv_heads * (head_dim + v_dim)), head_dim, v_dim
+
+
+def kv_store(k, v, token_entry, positions, block_table, cache, n_tokens=None, kv_heads=None, head_dim=None, v_dim=None):
+    """k: [N, kv_heads*head_dim], v: [N, kv_heads*v_dim] views (row stride free); cache: see cache_geometry."""
+    n_pages, kv_heads, page_size, head_dim, v_dim = cache_geometry(cache, kv_heads, head_dim, v_dim)
     if k.stride(0) != v.stride(0) or k.stride(1) != 1 or v.stride(1) != 1 or k.dtype != cache.dtype:
         raise KernelError("kv_store: k and v must be row views of one buffer in the cache dtype")
-    if k.shape[1] != kv_heads * head_dim or not cache.is_contiguous():
+    if k.shape[1] != kv_heads * head_dim or v.shape[1] != kv_heads * v_dim or not cache.is_contiguous():
         raise KernelError("kv_store: shapes do not fit the cache")
     _call(library("core"), "dd_kv_store", _ptr(k, "k"), _ptr(v, "v"), k.stride(0),
           _ptr(token_entry, "token_entry", torch.int32), _ptr(positions, "positions", torch.int32),
           _ptr(block_table, "block_table", torch.int32), block_table.shape[1], _ptr(cache, "cache"),
-          n_pages, kv_heads, page_size, head_dim, k.shape[0] if n_tokens is None else n_tokens, _dt(cache.dtype),
+          n_pages, kv_heads, page_size, head_dim, v_dim, k.shape[0] if n_tokens is None else n_tokens, _dt(cache.dtype),
           _ptr(error_flag(k.device)), _stream())
 
 
-def attention_rows(q, cache, token_entry, positions, block_table, n_heads, scale, window=None, n_splits=1, out=None):
-    """General paged causal attention. q: [N, n_heads*head_dim] view; returns [N, n_heads*head_dim]."""
-    n_pages, _, kv_heads, page_size, head_dim = cache.shape
+def attention_rows(q, cache, token_entry, positions, block_table, n_heads, scale, window=None, n_splits=1, out=None,
+                   chunk=None, gate=None, kv_heads=None, v_dim=None):
+    """General paged causal attention. q: [N, n_heads*head_dim] view; returns [N, n_heads*v_dim]. chunk: positions
+    are cut into chunks of this many from the start of the sequence and nothing is seen across a border. gate:
+    [N, n_heads] view, a head's output is multiplied by the logistic function of its entry. kv_heads and v_dim name the
+    sizes of a cache whose value heads differ from its key heads (see cache_geometry)."""
+    head_dim = q.shape[1] // n_heads
+    n_pages, kv_heads, page_size, head_dim, v_dim = cache_geometry(cache, kv_heads, head_dim, v_dim)
     n = q.shape[0]
     if q.shape[1] != n_heads * head_dim or q.stride(1) != 1 or q.dtype != cache.dtype or not cache.is_contiguous():
         raise KernelError("attention: q does not fit the cache")
+    if gate is not None and (gate.shape != (n, n_heads) or gate.stride(1) != 1 or gate.dtype != q.dtype):
+        raise KernelError("attention: the gate must be a [tokens, heads] row view in q's dtype")
     if out is None:
-        out = torch.empty((n, n_heads * head_dim), dtype=q.dtype, device=q.device)
+        out = torch.empty((n, n_heads * v_dim), dtype=q.dtype, device=q.device)
     part_o = part_ml = None
     if n_splits > 1:
-        part_o = torch.empty((n * n_heads * n_splits * head_dim,), dtype=torch.float32, device=q.device)
+        part_o = torch.empty((n * n_heads * n_splits * v_dim,), dtype=torch.float32, device=q.device)
         part_ml = torch.empty((n * n_heads * n_splits * 2,), dtype=torch.float32, device=q.device)
-    _call(library("core"), "dd_attention_rows", _ptr(q, "q"), q.stride(0), _ptr(cache, "cache"),
+    _call(library("core"), "dd_attention_rows_masked", _ptr(q, "q"), q.stride(0), _ptr(cache, "cache"),
           _ptr(token_entry, "token_entry", torch.int32), _ptr(positions, "positions", torch.int32),
           _ptr(block_table, "block_table", torch.int32), block_table.shape[1], _ptr(out, "out"), out.stride(0),
           _ptr(part_o), _ptr(part_ml), n, n_heads, kv_heads, head_dim, page_size, n_pages,
           0 if window is None else int(window), float(scale), int(n_splits), _dt(q.dtype),
-          _ptr(error_flag(q.device)), _stream(), n_kernels=2 if n_splits > 1 else 1)
+          _ptr(error_flag(q.device)), _stream(), v_dim, 0 if chunk is None else int(chunk), _ptr(gate, "gate"),
+          0 if gate is None else gate.stride(0), n_kernels=2 if n_splits > 1 else 1)
     return out
+
+
+# ---- experts chosen by a table: routing, the grouped product, the gated unit, the weighted sum ----
+
+def grouped_rows(n_tokens, top, n_experts, tile):
+    """Rows of the buffer in which every expert's (token, choice) pairs start on a multiple of tile."""
+    pairs = n_tokens * top
+    return -(-(pairs + min(n_experts, pairs) * (tile - 1)) // tile) * tile
+
+
+def route_by_table(ids, table, n_experts, tile):
+    """ids int32 [N], table int32 [vocab, K] -> (pair_row [N*K], row_token [rows], tile_group [rows/tile])."""
+    n, (vocab, top) = ids.numel(), table.shape
+    rows = grouped_rows(n, top, n_experts, tile)
+    pair_row = torch.empty((n * top,), dtype=torch.int32, device=ids.device)
+    row_token = torch.empty((rows,), dtype=torch.int32, device=ids.device)
+    tile_group = torch.empty((rows // tile,), dtype=torch.int32, device=ids.device)
+    _call(library("core"), "dd_route_by_table", _ptr(ids, "ids", torch.int32), _ptr(table, "table", torch.int32), n, vocab, top,
+          n_experts, tile, rows, _ptr(pair_row), _ptr(row_token), _ptr(tile_group), _ptr(error_flag(ids.device)), _stream())
+    return pair_row, row_token, tile_group
+
+
+def gather_rows(x, row_token):
+    """out[r] = x[row_token[r]], zeros where row_token[r] < 0."""
+    _rows(x, "x")
+    out = torch.empty((row_token.numel(), x.shape[1]), dtype=x.dtype, device=x.device)
+    if not x.is_contiguous():
+        raise KernelError("gather_rows input must be contiguous")
+    _call(library("core"), "dd_gather_rows", _ptr(x, "x"), _ptr(row_token, "row_token", torch.int32), _ptr(out), row_token.numel(),
+          x.shape[1], _dt(x.dtype), _stream())
+    return out
+
+
+def simt_group_tile():
+    return int(library("core").dd_gemm_simt_group_tile())
+
+
+def gemm_simt_grouped(a, w, tile_group, activation=None, out_dtype=None):
+    """a [rows, K] in tiles of simt_group_tile() rows; w [groups, N, K]; tile i is multiplied with w[tile_group[i]]
+    (skipped where that is negative). CUDA-core float32 multiply-add, k ascending."""
+    _rows(a, "a")
+    if w.dim() != 3 or not w.is_contiguous() or w.shape[2] != a.shape[1] or w.dtype != a.dtype:
+        raise KernelError(f"grouped gemm: a {tuple(a.shape)} {a.dtype} does not fit w {tuple(w.shape)} {w.dtype}")
+    M, K = a.shape
+    N = w.shape[1]
+    out_dtype = out_dtype or a.dtype
+    out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    _call(library("core"), "dd_gemm_simt_grouped", _ptr(a, "a"), a.stride(0), _ptr(w, "w"), w.stride(1), w.stride(0),
+          _ptr(tile_group, "tile_group", torch.int32), _ptr(out), out.stride(0), M, N, K, ACTIVATIONS[activation],
+          _dt(a.dtype), _dt(out_dtype), _stream())
+    return out
+
+
+def gated_unit(gate_up, limit, alpha, out=None):
+    """rows of [gate | up] halves -> min(gate, limit) * sigmoid(alpha * min(gate, limit)) * (clamp(up, -limit, limit) + 1)."""
+    _rows(gate_up, "gate_up")
+    rows, inner = gate_up.shape[0], gate_up.shape[1] // 2
+    if out is None:
+        out = torch.empty((rows, inner), dtype=gate_up.dtype, device=gate_up.device)
+    _call(library("core"), "dd_gated_unit", _ptr(gate_up, "gate_up"), gate_up.stride(0), _ptr(out), out.stride(0), rows, inner,
+          float(limit), float(alpha), _dt(gate_up.dtype), _stream())
+    return out
+
+
+def combine_rows(y, pair_row, stream_rows, top, weight):
+    """stream_rows[t] += weight * sum over k of y[pair_row[t*top + k]] (float32, k ascending), in place."""
+    if y.dtype != torch.float32 or stream_rows.dtype != torch.float32 or not y.is_contiguous() or not stream_rows.is_contiguous():
+        raise KernelError("combine_rows: float32 contiguous rows wanted")
+    _call(library("core"), "dd_combine_rows", _ptr(y), _ptr(pair_row, "pair_row", torch.int32), _ptr(stream_rows),
+          stream_rows.shape[0], stream_rows.shape[1], int(top), float(weight), _stream())
+    return stream_rows
 
 
 def sample(logits, temperature=None, uniform=None, top_k=None, top_p=None, out=None):

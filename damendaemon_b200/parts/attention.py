@@ -1,9 +1,13 @@
 """The attention mixer: fused QKV projection, cache write, paged causal attention, output
 projection with the residual add in its epilogue (damendaemon/gpt2.py:48-61).
 
-Heads, key/value groups, head size, scale and window are parameters of the spec. The
-kernels read keys and values from the cache pages only, so a portion of a prompt sees
-earlier portions exactly as a decoded token sees its context.
+Heads, key/value groups, head size, scale and window are parameters of the spec, and so
+are: a value head of another size than a key head; a chunked mask (positions in chunks
+counted from the start of the sequence, nothing seen across a border); a gate per head,
+sigmoid of one more projection of the mixer's input, on the head's output before the
+output projection (its rows are joined to the fused projection); a rotary position
+encoding of the mixer's own. The kernels read keys and values from the cache pages only, so
+a portion of a prompt sees earlier portions exactly as a decoded token sees its context.
 """
 from __future__ import annotations
 
@@ -13,7 +17,7 @@ from ..cache.manager import PagedKeyValues
 from .paged_attention import prompt_key_block
 from .interfaces import Mixer
 from .linear import linear
-from .registry import register_mixer
+from .registry import POSITIONS, lookup, register_mixer
 from .spec import TensorDecl
 
 
@@ -22,39 +26,62 @@ def _joined(names):
     return names if isinstance(names, str) else "+".join(names)
 
 
+def _projection(spec):
+    """(names of the pieces of the fused projection, or its one name; the key the joined tensor is found under)."""
+    names = spec.qkv_weight
+    if spec.gate_weight:
+        if isinstance(names, str):
+            raise ValueError("a gate's rows are joined to separate query, key and value projections")
+        names = tuple(names) + (spec.gate_weight,)
+    return names, _joined(names)
+
+
 @register_mixer("attention")
 class Attention(Mixer):
     graph_safe = True
 
     def __init__(self, spec, weights, runtime):
         self.spec, self.runtime = spec, runtime
-        self.qkv_w = weights[_joined(spec.qkv_weight)]
+        self.qkv_w = weights[_projection(spec)[1]]
         self.qkv_b = weights[_joined(spec.qkv_bias)] if spec.qkv_bias else None
         self.out_w = weights[spec.out_weight]
         self.out_b = weights[spec.out_bias] if spec.out_bias else None
+        self.value_dim = spec.value_dim or spec.head_dim
         self.q_width = spec.n_heads * spec.head_dim
         self.kv_width = spec.n_kv_heads * spec.head_dim
-        if spec.head_dim % 8 or spec.head_dim > 256:
+        self.v_width = spec.n_kv_heads * self.value_dim
+        plain = self.value_dim == spec.head_dim
+        if spec.head_dim > 256 or self.value_dim > 256 or (plain and spec.head_dim % 8):
             raise ValueError(f"head size {spec.head_dim} is not supported (multiples of 8 up to 256)")
+        if spec.gate_weight and spec.qkv_bias:
+            raise ValueError("a gated attention with projection biases is not supported")
+        self.rotary = None if spec.rotary is None else lookup(POSITIONS, spec.rotary, "position encoding")(spec.rotary, weights, runtime)
+        # what the attention kernels are told beside heads, scale and window
+        self.mask = dict(chunk=spec.chunk, value_dim=None if plain else self.value_dim)
         if spec.n_heads % spec.n_kv_heads:
             raise ValueError(f"{spec.n_heads} heads cannot share {spec.n_kv_heads} key/value heads")
         # where this mixer likes a prompt to be cut: the key block of its prompt kernel, if that kernel takes its sizes
         self.portion_multiple = 1
-        if runtime.dtype == torch.bfloat16 and runtime.attention == "auto" and runtime.gemm != "simt":
+        if runtime.dtype == torch.bfloat16 and runtime.attention == "auto" and runtime.gemm != "simt" and plain \
+                and not spec.chunk and not spec.gate_weight:
             self.portion_multiple = prompt_key_block(spec.n_heads, spec.n_kv_heads, spec.head_dim, runtime.page_size, runtime.dtype)
 
     @staticmethod
     def tensor_decls(spec):
         q, kv = spec.n_heads * spec.head_dim, spec.n_kv_heads * spec.head_dim
-        total = q + 2 * kv
+        v = spec.n_kv_heads * (spec.value_dim or spec.head_dim)
+        gate = spec.n_heads if spec.gate_weight else 0
+        total = q + kv + v + gate
         io = spec.stored_in_out
         matrix = lambda n: (spec.width, n) if io else (n, spec.width)
-        # one fused projection in the checkpoint, or separate query, key and value projections joined at load
-        pieces = () if isinstance(spec.qkv_weight, str) else tuple(zip(spec.qkv_weight, (matrix(q), matrix(kv), matrix(kv))))
-        decls = [TensorDecl(_joined(spec.qkv_weight), matrix(total), "matrix", io, pieces),
-                 TensorDecl(spec.out_weight, (q, spec.width) if io else (spec.width, q), "matrix", io)]
+        # one fused projection in the checkpoint, or separate query, key and value (and gate) projections joined at load
+        names, key = _projection(spec)
+        pieces = () if isinstance(names, str) else tuple(zip(names, (matrix(q), matrix(kv), matrix(v), matrix(gate))))
+        decls = [TensorDecl(key, matrix(total), "matrix", io, pieces),
+                 TensorDecl(spec.out_weight, (spec.n_heads * v // spec.n_kv_heads, spec.width) if io
+                            else (spec.width, spec.n_heads * v // spec.n_kv_heads), "matrix", io)]
         if spec.qkv_bias:
-            pieces = () if isinstance(spec.qkv_bias, str) else tuple(zip(spec.qkv_bias, ((q,), (kv,), (kv,))))
+            pieces = () if isinstance(spec.qkv_bias, str) else tuple(zip(spec.qkv_bias, ((q,), (kv,), (v,))))
             decls.append(TensorDecl(_joined(spec.qkv_bias), (total,), "vector", False, pieces))
         if spec.out_bias:
             decls.append(TensorDecl(spec.out_bias, (spec.width,), "vector"))
@@ -62,15 +89,19 @@ class Attention(Mixer):
 
     @staticmethod
     def cache_needs(spec):
-        return [PagedKeyValues(spec.n_kv_heads, spec.head_dim, spec.window)]
+        value_dim = None if spec.value_dim in (None, spec.head_dim) else spec.value_dim
+        return [PagedKeyValues(spec.n_kv_heads, spec.head_dim, spec.window, value_dim, spec.chunk)]
 
     def forward(self, y, residual, ctx, cache, position):
         s = self.spec
         qkv = linear(self.runtime, y, self.qkv_w, self.qkv_b)
         q = qkv[:, :self.q_width]
         k = qkv[:, self.q_width:self.q_width + self.kv_width]
-        v = qkv[:, self.q_width + self.kv_width:]
+        v = qkv[:, self.q_width + self.kv_width:self.q_width + self.kv_width + self.v_width]
+        gate = qkv[:, self.q_width + self.kv_width + self.v_width:] if s.gate_weight else None
         q, k = position.on_query_key(q, k, ctx)
-        attended = ctx.attend(q, k, v, cache, s.n_heads, s.scale, s.window)
+        if self.rotary is not None:
+            q, k = self.rotary.on_query_key(q, k, ctx)
+        attended = ctx.attend(q, k, v, cache, s.n_heads, s.scale, s.window, gate=gate, **self.mask)
         return linear(self.runtime, attended, self.out_w, self.out_b, residual=residual, out_dtype=residual.dtype,
                       out=residual)

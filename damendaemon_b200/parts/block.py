@@ -1,6 +1,7 @@
 """Block arrangements: how a layer's norms, mixer and feed-forward are wired.
 
 'pre_norm': x = x + mixer(norm[0](x)); x = x + feed_forward(norm[1](x))  (damendaemon/gpt2.py:47-64).
+'pre_norm_mixer': x = x + mixer(norm[0](x)), a layer without a feed-forward.
 """
 from __future__ import annotations
 
@@ -17,3 +18,14 @@ class PreNormBlock:
     def forward(self, x, ctx, cache, position):
         x = self.mixer.forward(self.norms[0].forward(x), x, ctx, cache, position)
         return self.feed_forward.forward(self.norms[1].forward(x), x, ctx)
+
+
+@register_arrangement("pre_norm_mixer")
+class PreNormMixerOnly:
+    def __init__(self, spec, norms, mixer, feed_forward):
+        if len(norms) != 1:
+            raise ValueError(f"a mixer-only block takes one norm, got {len(norms)}")
+        self.spec, self.norms, self.mixer, self.feed_forward = spec, list(norms), mixer, feed_forward
+
+    def forward(self, x, ctx, cache, position):
+        return self.mixer.forward(self.norms[0].forward(x), x, ctx, cache, position)

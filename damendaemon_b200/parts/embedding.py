@@ -1,6 +1,6 @@
 """Embeddings: from the step's token ids to the float32 residual stream.
 
-'tokens': x[t] = table[id[t]] (+ the position encoding's own table at the token's position, if it has one:
+'tokens': x[t] = table[id[t]] * scale (+ the position encoding's own table at the token's position, if it has one:
 damendaemon/gpt2.py:46), one fused gather; the position encoding may then act on x (``on_embedding``).
 """
 from __future__ import annotations
@@ -21,5 +21,5 @@ class TokenEmbedding(Embedding):
         return [TensorDecl(spec.table, (spec.vocab_size, spec.width), "table")]
 
     def forward(self, ctx, position):
-        x = kernels.embed(ctx.token_ids, ctx.positions, self.table, position.embedding_table())
+        x = kernels.embed(ctx.token_ids, ctx.positions, self.table, position.embedding_table(), scale=self.spec.scale)
         return position.on_embedding(x, ctx)

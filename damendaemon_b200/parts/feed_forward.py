@@ -1,13 +1,19 @@
 """Feed-forwards. Dense two-matrix MLP with the activation fused into the first product's
-epilogue and the residual add into the second's (damendaemon/gpt2.py:62-64)."""
+epilogue and the residual add into the second's (damendaemon/gpt2.py:62-64). Experts chosen by a
+table of token ids: small gated units, a token's chosen ones weighted equally, a shared one for every
+token; their products run grouped, expert by expert, over rows sorted on the device. 'none': a layer
+without a feed-forward."""
 from __future__ import annotations
 
+import torch
+
+from .. import kernels
 from .interfaces import FeedForward
-from .linear import linear
+from .linear import grouped_linear, grouped_tile, linear
 from .registry import register_feed_forward
 from .spec import TensorDecl
 
-ACTIVATIONS = ("gelu_new", "gelu")
+ACTIVATIONS = ("gelu_new", "gelu", "relu2")
 
 
 @register_feed_forward("dense")
@@ -37,3 +43,77 @@ class DenseFeedForward(FeedForward):
         hidden = linear(self.runtime, y, self.up_w, self.up_b, activation=self.spec.activation)
         return linear(self.runtime, hidden, self.down_w, self.down_b, residual=residual, out_dtype=residual.dtype,
                       out=residual)
+
+
+@register_feed_forward("none")
+class NoFeedForward(FeedForward):
+    graph_safe = True
+
+    def __init__(self, spec, weights, runtime):
+        self.spec = spec
+
+    def forward(self, y, residual, ctx):
+        return residual
+
+
+def _unit_decls(unit, width):
+    return [TensorDecl(unit.gate_weight, (unit.inner, width), "matrix"),
+            TensorDecl(unit.up_weight, (unit.inner, width), "matrix"),
+            TensorDecl(unit.down_weight, (width, unit.inner), "matrix")]
+
+
+@register_feed_forward("experts_by_table")
+class TableRoutedExperts(FeedForward):
+    """out = residual + (1/K) sum over the K experts of row ids[t] of the table of unit_e(y) + shared(y).
+
+    The experts' gate and up matrices are stacked [E, 2 * inner, width] (gate rows, then up rows) and their down
+    matrices [E, width, inner] once, when the part is built. A step sorts its (token, choice) pairs by expert on the
+    device (kernels.route_by_table: every expert's rows start on a multiple of the product's row tile), gathers the
+    normed rows in that order, runs two grouped products with the gated unit between, and adds each token's rows,
+    in the order of its choices, into the float32 stream. Launch shapes depend on the step's counts only, so a step
+    can be replayed from a graph."""
+    graph_safe = True
+
+    def __init__(self, spec, weights, runtime):
+        self.spec, self.runtime = spec, runtime
+        first = spec.experts[0]
+        if any((u.inner, u.limit, u.alpha) != (first.inner, first.limit, first.alpha) for u in spec.experts):
+            raise ValueError("the experts of one layer must have one size, limit and slope")
+        if not 0 < spec.top <= len(spec.experts):
+            raise ValueError(f"{spec.top} experts per token of {len(spec.experts)}")
+        self.table = weights[spec.table]
+        self.gate_up = torch.stack([torch.cat([weights[u.gate_weight], weights[u.up_weight]], dim=0) for u in spec.experts])
+        self.down = torch.stack([weights[u.down_weight] for u in spec.experts])
+        # the stacks take the place of the single matrices (one copy on the device, and in the engine's count of bytes)
+        for u in spec.experts:
+            for name in (u.gate_weight, u.up_weight, u.down_weight):
+                weights.pop(name, None)
+        weights[spec.table + ":gate_up"], weights[spec.table + ":down"] = self.gate_up, self.down
+        self.shared = None
+        if spec.shared is not None:
+            u = spec.shared
+            self.shared = (torch.cat([weights[u.gate_weight], weights[u.up_weight]], dim=0).contiguous(), weights[u.down_weight])
+
+    @staticmethod
+    def tensor_decls(spec):
+        decls = [TensorDecl(spec.table, (spec.vocab_size, spec.top), "int")]
+        for unit in spec.experts:
+            decls += _unit_decls(unit, spec.width)
+        if spec.shared is not None:
+            decls += _unit_decls(spec.shared, spec.width)
+        return decls
+
+    def forward(self, y, residual, ctx):
+        s, rt = self.spec, self.runtime
+        unit = s.experts[0]
+        if self.shared is not None:
+            gate_up = linear(rt, y, self.shared[0])
+            hidden = kernels.gated_unit(gate_up, s.shared.limit, s.shared.alpha)
+            residual = linear(rt, hidden, self.shared[1], residual=residual, out_dtype=residual.dtype, out=residual)
+        tile = grouped_tile(rt, y)
+        pair_row, row_token, tile_group = kernels.route_by_table(ctx.token_ids, self.table, len(s.experts), tile)
+        rows = kernels.gather_rows(y, row_token)
+        gate_up = grouped_linear(rt, rows, self.gate_up, tile_group, tile)
+        hidden = kernels.gated_unit(gate_up, unit.limit, unit.alpha)
+        out = grouped_linear(rt, hidden, self.down, tile_group, tile, out_dtype=torch.float32)
+        return kernels.combine_rows(out, pair_row, residual, s.top, 1.0 / s.top)

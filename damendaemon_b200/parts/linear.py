@@ -16,3 +16,14 @@ def linear(runtime, a, w, bias=None, residual=None, activation=None, out_dtype=N
         # TMA wants 16-byte rows; a reduction width that is no multiple of 8 runs on the CUDA cores instead
         return kernels.gemm_simt(a, w, bias, residual, activation, out_dtype or torch.bfloat16, out)
     return kernels.gemm_tcgen05(a, w, bias, residual, activation, out_dtype, out)
+
+
+def grouped_tile(runtime, a):
+    """Rows per tile of the grouped product that ``grouped_linear`` will run for rows like a."""
+    return kernels.simt_group_tile()
+
+
+def grouped_linear(runtime, a, w, tile_group, tile, out_dtype=None):
+    """Rows of a in tiles of ``tile``; tile i is multiplied with w[tile_group[i]] (w: [groups, out, in]); tiles whose
+    group is negative are skipped."""
+    return kernels.gemm_simt_grouped(a, w, tile_group, out_dtype=out_dtype or a.dtype)

@@ -1,4 +1,5 @@
-"""Norms. LayerNorm with weight and optional bias (damendaemon/starcoder.py:53-55)."""
+"""Norms. LayerNorm with weight and optional bias (damendaemon/starcoder.py:53-55); RMS norm,
+x / sqrt(mean(x^2) + eps) * (offset + weight), with the offset a parameter of the spec."""
 from __future__ import annotations
 
 from .. import kernels
@@ -23,3 +24,20 @@ class LayerNorm(Norm):
 
     def forward(self, x, row_index=None, out_dtype=None):
         return kernels.layernorm(x, self.gamma, self.beta, self.spec.eps, out_dtype or self.runtime.dtype, row_index)
+
+
+@register_norm("rmsnorm")
+class RmsNorm(Norm):
+    def __init__(self, spec, weights, runtime):
+        if spec.bias:
+            raise ValueError("an RMS norm has no bias")
+        self.spec, self.runtime = spec, runtime
+        self.weight = weights[spec.weight]
+
+    @staticmethod
+    def tensor_decls(spec):
+        return [TensorDecl(spec.weight, (spec.width,), "vector")]
+
+    def forward(self, x, row_index=None, out_dtype=None):
+        return kernels.rmsnorm(x, self.weight, self.spec.eps, out_dtype or self.runtime.dtype, row_index,
+                               offset=self.spec.weight_offset)

@@ -35,19 +35,31 @@ def prompt_key_block(n_heads, kv_heads, head_dim, page_size, dtype):
     return 1
 
 
-def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None):
+def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None, chunk=None, gate=None, value_dim=None):
     runtime = ctx.runtime
     tune = runtime.attention_tuning
-    if not (q.stride(0) == k.stride(0) == v.stride(0)) or q.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1:
+    if not (q.stride(0) == k.stride(0) == v.stride(0)) or q.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1 or \
+            (gate is not None and (gate.stride(0) != q.stride(0) or gate.stride(1) != 1)):
         # the kernels read q, k and v as row views of one buffer (what a fused projection leaves); a part that made
         # new tensors of some of them (a position encoding that does not rotate in place) gets them packed again
         import torch
-        widths = (q.shape[1], k.shape[1], v.shape[1])
-        q, k, v = torch.cat([q, k, v], dim=1).split(widths, dim=1)
+        parts = [q, k, v] + ([gate] if gate is not None else [])
+        packed = torch.cat(parts, dim=1).split([p.shape[1] for p in parts], dim=1)
+        q, k, v = packed[:3]
+        gate = packed[3] if gate is not None else None
     kv, table = cache.kv, ctx.block_table(cache.group)
+    if value_dim is not None and value_dim != cache.group.need.head_dim:
+        need = cache.group.need
+        # value heads of their own size: the general kernel, which is told the page's geometry
+        if cache.writable:
+            kernels.kv_store(k, v, ctx.token_entry, ctx.positions, table, kv, kv_heads=need.kv_heads, head_dim=need.head_dim,
+                             v_dim=value_dim)
+        return kernels.attention_rows(q, kv, ctx.token_entry, ctx.positions, table, n_heads, scale, window,
+                                      n_splits=ctx.key_splits(n_heads), chunk=chunk, gate=gate, kv_heads=need.kv_heads,
+                                      v_dim=value_dim)
     kv_heads, page_size, head_dim = kv.shape[2], kv.shape[3], kv.shape[4]
     k_new, v_new = (k, v) if cache.writable else (None, None)
-    fast = runtime.attention != "rows"
+    fast = runtime.attention != "rows" and not chunk and gate is None
     tensor = fast and runtime.attention != "mma"
     def wants_pages(n_tokens):
         pairs = n_tokens * n_heads
@@ -101,4 +113,4 @@ def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None):
         return kernels.attention_prefill(q, kv, ctx.entry_start[n1:], ctx.entry_pos0[n1:], table[n1:], n_heads, scale, window,
                                          out=out)
     return kernels.attention_rows(q, kv, ctx.token_entry, ctx.positions, table, n_heads, scale, window,
-                                  n_splits=ctx.key_splits(n_heads))
+                                  n_splits=ctx.key_splits(n_heads), chunk=chunk, gate=gate)

@@ -36,11 +36,12 @@ class TensorDecl:
 
 @dataclass(frozen=True)
 class NormSpec:
-    kind: str            # 'layernorm'
+    kind: str            # 'layernorm' | 'rmsnorm'
     width: int
     eps: float
     weight: str          # checkpoint names
     bias: Optional[str] = None
+    weight_offset: float = 0.0   # 'rmsnorm': the factor is weight_offset + weight (1 for a weight stored around zero)
 
 
 @dataclass(frozen=True)
@@ -49,6 +50,28 @@ class PositionSpec:
     n_positions: int
     width: int
     table: Optional[str] = None
+
+
+@dataclass(frozen=True)
+class LongContextBlend:
+    """Rotary frequencies blended for contexts beyond the one a model was trained at (the YaRN rule): pair i keeps
+    its frequency f_i where its wavelength turns more than ``fast`` times over ``original`` tokens, gets f_i / factor
+    where it turns fewer than ``slow`` times, a linear blend between; cosine and sine are scaled by
+    0.1 ln(factor) + 1."""
+    factor: float
+    original: float
+    fast: float
+    slow: float
+
+
+@dataclass(frozen=True)
+class RotarySpec:
+    kind: str            # 'rotary'
+    head_dim: int
+    dims: int            # the first `dims` dimensions of a head are rotated, the rest pass unchanged
+    base: float
+    interleaved: bool = True     # pairs are neighbours (2i, 2i+1); False: halves (i, i + dims/2)
+    blend: Optional[LongContextBlend] = None
 
 
 @dataclass(frozen=True)
@@ -65,6 +88,10 @@ class AttentionSpec:
     out_weight: str
     out_bias: Optional[str]
     stored_in_out: bool = False
+    value_dim: Optional[int] = None   # size of a value head where it differs from head_dim
+    chunk: Optional[int] = None       # positions in chunks of this many from the start; nothing is seen across a border
+    gate_weight: Optional[str] = None  # [n_heads, width]: a head's output is multiplied by sigmoid(gate . input)
+    rotary: object = None             # a position-encoding spec of the mixer's own (applied to its queries and keys)
 
 
 @dataclass(frozen=True)
@@ -72,7 +99,7 @@ class DenseFeedForwardSpec:
     kind: str            # 'dense'
     width: int
     inner: int
-    activation: str      # 'gelu_new' | 'gelu'
+    activation: str      # 'gelu_new' | 'gelu' | 'relu2'
     up_weight: str
     up_bias: Optional[str]
     down_weight: str
@@ -81,9 +108,38 @@ class DenseFeedForwardSpec:
 
 
 @dataclass(frozen=True)
+class GatedUnitSpec:
+    """A small feed-forward with a clamped gate: g = min(W_gate y, limit), u = clamp(W_up y, -limit, limit),
+    output W_down (g * sigmoid(alpha g) * (u + 1)). No biases."""
+    inner: int
+    limit: float
+    gate_weight: str
+    up_weight: str
+    down_weight: str
+    alpha: float = 1.702
+
+
+@dataclass(frozen=True)
+class TableRoutedExpertsSpec:
+    kind: str            # 'experts_by_table'
+    width: int
+    vocab_size: int
+    top: int             # experts per token; each weighs 1 / top
+    table: str           # checkpoint name of the integer table [vocab, top]: a token id's experts
+    experts: Tuple[GatedUnitSpec, ...]       # all of one size and limit
+    shared: Optional[GatedUnitSpec] = None   # runs for every token and is added
+
+
+@dataclass(frozen=True)
+class NoFeedForwardSpec:
+    kind: str = "none"
+
+
+@dataclass(frozen=True)
 class LayerSpec:
     """A layer: a mixer, a feed-forward, as many norms as its arrangement wants, and the arrangement that wires them
-    ('pre_norm' takes two norms: before the mixer, before the feed-forward)."""
+    ('pre_norm' takes two norms: before the mixer, before the feed-forward; 'pre_norm_mixer' one norm and no
+    feed-forward)."""
     arrangement: str
     mixer: object
     feed_forward: object
@@ -100,6 +156,7 @@ class EmbeddingSpec:
     vocab_size: int
     width: int
     table: str           # checkpoint name
+    scale: float = 1.0   # multiplies the row
 
 
 @dataclass(frozen=True)
@@ -131,7 +188,7 @@ class ModelSpec:
     architecture: str
     vocab_size: int
     width: int
-    max_positions: int
+    max_positions: Optional[int]      # None: the architecture sets no limit (the engine's cache does)
     embedding: object                 # an embedding spec
     position: object                  # a position-encoding spec
     layers: Tuple[LayerSpec, ...]

@@ -1,6 +1,6 @@
 """The one registry from an architecture's name to its configuration and model.
 
-``config.json``'s ``architectures[0]`` selects the entry everywhere in the framework
+``config.json``'s ``architectures[0]`` (or its ``architecture``, where a model names one so) selects the entry everywhere in the framework
 (engine, command line, trace replay, random-weights writer). The reference
 dispatches on ``model_type`` in three places (damendaemon/config.py:119-145,
 damendaemon/runtime.py:675-679, damendaemon/qwen2.py:195-196); here it is one table.
@@ -33,6 +33,8 @@ def register_architecture(entry: Architecture, *, replace=False):
 
 def architecture_of(config: dict) -> Architecture:
     names = config.get("architectures")
+    if names is None and isinstance(config.get("architecture"), str):
+        names = [config["architecture"]]
     if not isinstance(names, list) or len(names) != 1 or not isinstance(names[0], str):
         raise ConfigError(f"config.json 'architectures' must name exactly one architecture, got {names!r}")
     _load_builtin()
@@ -49,4 +51,4 @@ def load_config(model_dir):
 
 
 def _load_builtin():
-    from .architectures import gpt2  # noqa: F401  (registers itself on import)
+    from .architectures import bonatar, gpt2  # noqa: F401  (register themselves on import)

@@ -25,10 +25,11 @@ class Runtime:
         prefill_chunk_size: largest prompt portion per step, 0 = up to the token budget.
         run_ahead: launch the next decode step before this step's tokens are read (see the scheduler).
         queue_timeout: seconds a request may wait for cache pages before it fails (None: no limit)."""
+        positions = _positions(model, config) or context or Engine.UNBOUNDED_CONTEXT   # a model may name no limit
         self.engine = Engine(model, config=config, tensors=tensors, dtype=dtype, page_size=page_size,
                              max_requests=max_batch, device=device,
-                             kv_tokens=kv_cache_tokens or max_batch * min(context or 10 ** 9, _positions(model, config)),
-                             check_device_errors=False, use_graph=use_graph)
+                             kv_tokens=kv_cache_tokens or max_batch * min(context or 10 ** 9, positions),
+                             check_device_errors=False, use_graph=use_graph, max_context=min(context or positions, positions))
         self.context = min(context or self.engine.max_context, self.engine.max_context)
         self.prefill_chunk_size = prefill_chunk_size
         self.token_budget = token_budget

@@ -43,11 +43,12 @@ class Recorder:
         self.calls.append(("prefill-" + kernel, entry_pos0.numel(), bool(store_new), table.shape[0]))
         return out if out is not None else q
 
-    def attention_rows(self, q, kv, token_entry, positions, table, n_heads, scale, window=None, n_splits=1, out=None):
+    def attention_rows(self, q, kv, token_entry, positions, table, n_heads, scale, window=None, n_splits=1, out=None,
+                       chunk=None, gate=None, kv_heads=None, v_dim=None):
         self.calls.append(("rows", q.shape[0], n_splits))
         return q
 
-    def kv_store(self, k, v, token_entry, positions, table, kv):
+    def kv_store(self, k, v, token_entry, positions, table, kv, **geometry):
         self.calls.append(("kv_store", k.shape[0]))
 
 
