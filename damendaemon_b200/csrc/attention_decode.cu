@@ -77,7 +77,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                         const int* __restrict__ block_table, int max_blocks, __nv_bfloat16* __restrict__ out,
                         int out_stride, float* __restrict__ part_o, float* __restrict__ part_ml,
                         int* __restrict__ counters, int H, int P, int n_pages, int window, float scale_log2e,
-                        int* __restrict__ error_flag) {
+                        int* __restrict__ error_flag, int chunk, const __nv_bfloat16* __restrict__ gate, int gate_stride) {
     constexpr int C = D / 8;            // 16-byte chunks (and lanes) per key row
     constexpr int KPL = 32 / C;         // keys per copy instruction of a warp
     constexpr int STEPS = TILE / KPL;   // copy instructions of K (and of V) per lane and stage
@@ -97,13 +97,16 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     const int c = lane % C, kg = lane / C;
     const int g = lane >> 2, t4 = lane & 3;
     const int pos = tok_pos[t];
-    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (chunk > 0) lo = max(lo, pos - pos % chunk);         // a chunked mask: nothing before the query's own chunk
     const int hi = pos + 1;
     int per = (hi - lo + n_splits - 1) / n_splits;
     per = (per + TILE - 1) / TILE * TILE;
     const int k0 = lo + split * per;
     const int k1 = min(hi, k0 + per);
     const int* bt = block_table + (size_t)(tok_entry ? tok_entry[t] : t) * max_blocks;     // no tok_entry: token t is entry t
+    // (the gate is the projection's output: it is read after the wait, where the result is stored)
+    float gated = 1.0f;
     for (int blk = k0 / P + (int)threadIdx.x * 32; blk < max_blocks && blk * P < k1 + 32 * P; blk += WARPS * 32 * 32)
         asm volatile("prefetch.global.L1 [%0];" ::"l"(bt + min(blk, max_blocks - 1)));
     const size_t head_plane = (size_t)P * D;
@@ -284,6 +287,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
     }
     __syncthreads();
     // combine the warps: thread d owns output dimension d
+    if (gate) gated = 1.0f / (1.0f + __expf(-__bfloat162float(gate[(size_t)t * gate_stride + h])));
     const size_t item = ((size_t)t * H + h) * n_splits + split;
     float M = -CUDART_INF_F;
 #pragma unroll
@@ -295,7 +299,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
         float acc = 0.f;
 #pragma unroll
         for (int w = 0; w < WARPS; ++w) acc += sh_ml[w][1] > 0.f ? sh_o[w][d] * exp2f(sh_ml[w][0] - M) : 0.f;
-        if (n_splits == 1) out[(size_t)t * out_stride + (size_t)h * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L : 0.f);
+        if (n_splits == 1) out[(size_t)t * out_stride + (size_t)h * D + d] = __float2bfloat16_rn(L > 0.f ? acc / L * gated : 0.f);
         else part_o[item * D + d] = acc;
     }
     STAMP(12);
@@ -342,7 +346,7 @@ attention_decode_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, const
                     acc += oo[u] * w;
                 }
         }
-        out[(size_t)t * out_stride + (size_t)h * D + d] = __float2bfloat16_rn(Lx > 0.f ? acc / Lx : 0.f);
+        out[(size_t)t * out_stride + (size_t)h * D + d] = __float2bfloat16_rn(Lx > 0.f ? acc / Lx * gated : 0.f);
     }
     if (threadIdx.x == 0) counters[t * H + h] = 0;
     STAMP(13);
@@ -362,12 +366,14 @@ DD_API int dd_attention_decode_supported(int n_heads, int n_kv_heads, int head_d
 // used for each token's own position and written to the cache here. part_o: float32
 // [n_tokens*heads*n_splits*head_dim], part_ml: float32 [n_tokens*heads*n_splits*2], counters: int32
 // [n_tokens*heads], zero before the first launch (the kernel leaves them zero); all three only when n_splits > 1.
+// chunk > 0: a query sees only the keys of its own chunk of that many positions (counted from position 0). gate: null,
+// or rows of gate_stride bf16 with one element per head, whose logistic function multiplies the head's output.
 DD_API int dd_attention_decode(const void* q, int q_stride, const void* k_new, const void* v_new, void* cache,
                                const int* tok_entry, const int* tok_pos,
                                const int* block_table, int max_blocks, void* out, int out_stride, float* part_o,
                                float* part_ml, int* counters, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                int page_size, int n_pages, int window, float scale, int n_splits, int* error_flag,
-                               void* stream) {
+                               void* stream, int chunk, const void* gate, int gate_stride) {
     if (n_tokens <= 0) return 0;
     if (!dd_attention_decode_supported(n_heads, n_kv_heads, head_dim, DD_BF16))
         return dd_fail("dd_attention_decode: needs heads == key/value heads and head size 64 or 128 (got %d, %d, %d)",
@@ -395,11 +401,11 @@ DD_API int dd_attention_decode(const void* q, int q_stride, const void* k_new, c
         dd_launch(attention_decode_kernel<64>, dim3(grid), dim3(WARPS * 32), RING, s, (const __nv_bfloat16*)q, q_stride,
             (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, (__nv_bfloat16*)cache,
             tok_entry, tok_pos, block_table, max_blocks, (__nv_bfloat16*)out, out_stride, part_o, part_ml, counters,
-            n_heads, page_size, n_pages, window, scale_log2e, error_flag);
+            n_heads, page_size, n_pages, window, scale_log2e, error_flag, chunk, (const __nv_bfloat16*)gate, gate_stride);
     else
         dd_launch(attention_decode_kernel<128>, dim3(grid), dim3(WARPS * 32), RING, s, (const __nv_bfloat16*)q, q_stride,
             (const __nv_bfloat16*)k_new, (const __nv_bfloat16*)v_new, (__nv_bfloat16*)cache,
             tok_entry, tok_pos, block_table, max_blocks, (__nv_bfloat16*)out, out_stride, part_o, part_ml, counters,
-            n_heads, page_size, n_pages, window, scale_log2e, error_flag);
+            n_heads, page_size, n_pages, window, scale_log2e, error_flag, chunk, (const __nv_bfloat16*)gate, gate_stride);
     return dd_check_launch("dd_attention_decode");
 }

@@ -41,6 +41,9 @@ struct Params {
     int* counters;
     int* error_flag;
     int q_stride, out_stride, max_blocks, H, G, P, n_pages, window, stages;
+    int chunk;                   // > 0: a query sees only the keys of its own chunk of this many positions
+    const __nv_bfloat16* gate;   // null, or rows of gate_stride elements, one per head: sigmoid(gate) multiplies the head's output
+    int gate_stride;
     int n_tokens, log2_P;
     int deal;                    // 1: more blocks in the grid than can be resident, so the splits are dealt out (see the kernel)
     float inv_block_budget;      // 1 / blocks that can be resident at once: the key splits are dealt out against them
@@ -98,7 +101,8 @@ attention_decode_pages_kernel(const __grid_constant__ CUtensorMap map_kv, const 
     const int span = p.max_blocks << p.log2_P;              // positions the block table can describe
     auto pages_of = [&](int position, int* first) {
         position = min(max(position, 0), span - 1);
-        const int from = p.window > 0 ? max(0, position - p.window + 1) : 0;
+        int from = p.window > 0 ? max(0, position - p.window + 1) : 0;
+        if (p.chunk > 0) from = max(from, position - position % p.chunk);
         if (first) *first = from >> p.log2_P;
         return (position >> p.log2_P) - (from >> p.log2_P) + 1;
     };
@@ -111,7 +115,8 @@ attention_decode_pages_kernel(const __grid_constant__ CUtensorMap map_kv, const 
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) total_pages += __shfl_xor_sync(0xffffffffu, total_pages, o);
     }
-    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    if (p.chunk > 0) lo = max(lo, pos - pos % p.chunk);
     int first_page = 0;
     const int my_pages = pages_of(pos, &first_page);
     const int last_page = first_page + my_pages - 1;
@@ -286,7 +291,8 @@ attention_decode_pages_kernel(const __grid_constant__ CUtensorMap map_kv, const 
         if (hl >= group_heads || quad != 0) continue;
         const int h = head0 + hl;
         if (n_splits == 1) {
-            const float inv = lu > 0.f ? 1.f / lu : 0.f;
+            float inv = lu > 0.f ? 1.f / lu : 0.f;
+            if (p.gate) inv *= 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[(size_t)t * p.gate_stride + h])));
             __nv_bfloat16* dst = p.out + (size_t)t * p.out_stride + (size_t)h * D + 2 * t4;
 #pragma unroll
             for (int j = 0; j < D / 8; ++j) *reinterpret_cast<uint32_t*>(dst + j * 8) = pack_bf16(o[u][j][0] * inv, o[u][j][1] * inv);
@@ -342,7 +348,8 @@ attention_decode_pages_kernel(const __grid_constant__ CUtensorMap map_kv, const 
                     acc += oo[u] * w;
                 }
         }
-        p.out[(size_t)t * p.out_stride + (size_t)h * D + d] = __float2bfloat16_rn(Lx > 0.f ? acc / Lx : 0.f);
+        const float gated = p.gate ? 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[(size_t)t * p.gate_stride + h]))) : 1.0f;
+        p.out[(size_t)t * p.out_stride + (size_t)h * D + d] = __float2bfloat16_rn(Lx > 0.f ? acc / Lx * gated : 0.f);
     }
     if (threadIdx.x == 0) p.counters[t * gridDim.y + g] = 0;
 }
@@ -404,7 +411,8 @@ DD_API int dd_attention_decode_pages(const void* q, int q_stride, const void* k_
                                      const int* tok_entry, const int* tok_pos, const int* block_table, int max_blocks,
                                      void* out, int out_stride, float* part_o, float* part_ml, int* counters, int n_tokens,
                                      int n_heads, int n_kv_heads, int head_dim, int page_size, int n_pages, int window,
-                                     float scale, int n_splits, int* error_flag, void* stream) {
+                                     float scale, int n_splits, int* error_flag, void* stream, int chunk, const void* gate,
+                                     int gate_stride) {
     if (n_tokens <= 0) return 0;
     if (!dd_attention_decode_pages_supported(n_heads, n_kv_heads, head_dim, page_size, DD_BF16))
         return dd_fail("dd_attention_decode_pages: needs heads == key/value heads, head size 64 and pages of 16, 32, 64 or 128 "
@@ -461,7 +469,8 @@ DD_API int dd_attention_decode_pages(const void* q, int q_stride, const void* k_
     p.cache = (__nv_bfloat16*)cache; p.tok_entry = tok_entry; p.tok_pos = tok_pos; p.block_table = block_table;
     p.out = (__nv_bfloat16*)out; p.part_o = part_o; p.part_ml = part_ml; p.counters = counters; p.error_flag = error_flag;
     p.q_stride = q_stride; p.out_stride = out_stride; p.max_blocks = max_blocks; p.H = n_heads; p.P = page_size;
-    p.n_pages = n_pages; p.window = window; p.scale_log2e = scale * 1.4426950408889634f;
+    p.n_pages = n_pages; p.window = window; p.chunk = chunk; p.gate = (const __nv_bfloat16*)gate; p.gate_stride = gate_stride;
+    p.scale_log2e = scale * 1.4426950408889634f;
     p.n_tokens = n_tokens;
     dd_launch(attention_decode_pages_kernel, dim3(n_tokens, n_groups, n_splits), dim3(THREADS), (size_t)smem, (cudaStream_t)stream, map, p);
     return dd_check_launch("dd_attention_decode_pages");

@@ -47,7 +47,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
                          const int* __restrict__ entry_start, const int* __restrict__ entry_pos0, int n_entries,
                          const int* __restrict__ block_table, int max_blocks, __nv_bfloat16* __restrict__ out,
                          int out_stride, int H, int KH, int P, int n_pages, int window, float scale_log2e,
-                         int* __restrict__ error_flag) {
+                         int* __restrict__ error_flag, int chunk, const __nv_bfloat16* __restrict__ gate, int gate_stride) {
     constexpr int NC = D / 8;                 // 16-byte chunks per row
     constexpr int KS = D / 16;                // k-steps over the head dimension
     extern __shared__ __align__(128) uint8_t smem[];
@@ -71,7 +71,13 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
     const int rows = min(BQ, len - q0);
     const int row0 = entry_start[e] + q0;
     const int pos_first = entry_pos0[e] + q0, pos_last = pos_first + rows - 1;
-    const int kv_lo = window > 0 ? max(0, pos_first - window + 1) : 0;
+    // the first key a query at pos sees: behind it the window, and with a chunked mask the start of its own chunk
+    auto first_seen = [&](int pos) {
+        int lo = window > 0 ? max(0, pos - window + 1) : 0;
+        if (chunk > 0) lo = max(lo, pos - pos % chunk);
+        return lo;
+    };
+    const int kv_lo = first_seen(pos_first);
     const int* bt = block_table + (size_t)e * max_blocks;
     const size_t head_plane = (size_t)P * D, page_stride = 2 * (size_t)KH * head_plane;
     const __nv_bfloat16* k_base = cache + (size_t)kh * head_plane;
@@ -124,7 +130,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
     const int qpos[2] = {pos_first + warp * 16 + g, pos_first + warp * 16 + g + 8};
     int qlo[2];
 #pragma unroll
-    for (int i = 0; i < 2; ++i) qlo[i] = window > 0 ? max(0, qpos[i] - window + 1) : 0;
+    for (int i = 0; i < 2; ++i) qlo[i] = first_seen(qpos[i]);
 
     for (int j = 0; j < n_tiles; ++j) {
         const int kb = kb_first + j * BKV, buf = j & 1;
@@ -157,7 +163,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
             }
         }
         // scale, mask, running maximum
-        const bool need_mask = (kb + BKV - 1 > pos_first + warp * 16) || window > 0 || kb < kv_lo;
+        const bool need_mask = (kb + BKV - 1 > pos_first + warp * 16) || window > 0 || chunk > 0 || kb < kv_lo;
         float mx[2] = {-CUDART_INF_F, -CUDART_INF_F};
 #pragma unroll
         for (int nt = 0; nt < 8; ++nt) {
@@ -225,7 +231,8 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
     for (int r = 0; r < 2; ++r) {
         const int row = warp * 16 + g + r * 8;
         if (row >= rows) continue;
-        const float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+        float inv = l[r] > 0.f ? 1.f / l[r] : 0.f;
+        if (gate) inv *= 1.0f / (1.0f + __expf(-__bfloat162float(gate[(size_t)(row0 + row) * gate_stride + h])));
         __nv_bfloat16* dst = out + (size_t)(row0 + row) * out_stride + (size_t)h * D + 2 * t4;
 #pragma unroll
         for (int i = 0; i < NC; ++i)
@@ -236,7 +243,7 @@ attention_prefill_kernel(const __nv_bfloat16* __restrict__ q, int q_stride, cons
 template <int D>
 int launch(const void* q, int q_stride, const void* cache, const int* entry_start, const int* entry_pos0, int n_entries,
            int n_tokens, const int* block_table, int max_blocks, void* out, int out_stride, int H, int KH, int P,
-           int n_pages, int window, float scale, int* error_flag, cudaStream_t s) {
+           int n_pages, int window, float scale, int* error_flag, cudaStream_t s, int chunk, const void* gate, int gate_stride) {
     constexpr int SMEM = (BQ + 4 * BKV) * D * 2;
     static bool configured = false;
     if (!configured) {
@@ -248,7 +255,7 @@ int launch(const void* q, int q_stride, const void* cache, const int* entry_star
     dim3 grid(dd_ceil_div(n_tokens, BQ) + n_entries, H);
     dd_launch(attention_prefill_kernel<D>, dim3(grid), dim3(THREADS), SMEM, s, (const __nv_bfloat16*)q, q_stride, (const __nv_bfloat16*)cache,
         entry_start, entry_pos0, n_entries, block_table, max_blocks, (__nv_bfloat16*)out, out_stride, H, KH, P, n_pages,
-        window, scale * 1.4426950408889634f, error_flag);
+        window, scale * 1.4426950408889634f, error_flag, chunk, (const __nv_bfloat16*)gate, gate_stride);
     return dd_check_launch("dd_attention_prefill");
 }
 }  // namespace
@@ -259,10 +266,13 @@ DD_API int dd_attention_prefill_supported(int n_heads, int n_kv_heads, int head_
 
 // Entries are runs of consecutive tokens of one request: entry e holds flattened tokens
 // entry_start[e] .. entry_start[e+1]-1 at positions entry_pos0[e] ... ; block_table row e is its pages.
+// chunk > 0: a query sees only the keys of its own chunk of that many positions (counted from position 0). gate: null,
+// or rows of gate_stride bf16 with one element per head, whose logistic function multiplies the head's output.
 DD_API int dd_attention_prefill(const void* q, int q_stride, const void* cache, const int* entry_start,
                                 const int* entry_pos0, int n_entries, int n_tokens, const int* block_table,
                                 int max_blocks, void* out, int out_stride, int n_heads, int n_kv_heads, int head_dim,
-                                int page_size, int n_pages, int window, float scale, int* error_flag, void* stream) {
+                                int page_size, int n_pages, int window, float scale, int* error_flag, void* stream,
+                                int chunk, const void* gate, int gate_stride) {
     if (n_tokens <= 0 || n_entries <= 0) return 0;
     if (!dd_attention_prefill_supported(n_heads, n_kv_heads, head_dim, DD_BF16))
         return dd_fail("dd_attention_prefill: needs head size 64 or 128 and heads a multiple of key/value heads (got %d, %d, %d)",
@@ -273,7 +283,7 @@ DD_API int dd_attention_prefill(const void* q, int q_stride, const void* cache, 
     cudaStream_t s = (cudaStream_t)stream;
     if (head_dim == 64)
         return launch<64>(q, q_stride, cache, entry_start, entry_pos0, n_entries, n_tokens, block_table, max_blocks, out,
-                          out_stride, n_heads, n_kv_heads, page_size, n_pages, window, scale, error_flag, s);
+                          out_stride, n_heads, n_kv_heads, page_size, n_pages, window, scale, error_flag, s, chunk, gate, gate_stride);
     return launch<128>(q, q_stride, cache, entry_start, entry_pos0, n_entries, n_tokens, block_table, max_blocks, out,
-                       out_stride, n_heads, n_kv_heads, page_size, n_pages, window, scale, error_flag, s);
+                       out_stride, n_heads, n_kv_heads, page_size, n_pages, window, scale, error_flag, s, chunk, gate, gate_stride);
 }

@@ -49,6 +49,9 @@ struct AttnParams {
     __nv_bfloat16* out;
     int* error_flag;
     int n_entries, max_blocks, out_stride, H, KH, P, n_pages, window;
+    int chunk;                   // > 0: a query sees only the keys of its own chunk of this many positions (from position 0)
+    const __nv_bfloat16* gate;   // null, or rows of gate_stride elements, one per head: sigmoid(gate) multiplies the head's output
+    int gate_stride;
     float scale_log2e;
     int new_rows;                   // 1: this step's keys and values are also at hand as rows beside the queries
     int store_new;                  // 1: the kernel itself puts those rows into the cache (every entry starts on a key-block boundary)
@@ -136,7 +139,12 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
     // (counted from the pair's first): the upper tile walks on where the lower one has met its diagonal
     auto tile_first = [&](int t) { return pos_first + t * BQ; };
     auto tile_last = [&](int t) { return min(pos_first + t * BQ + BQ - 1, pos_last); };
-    auto tile_lo = [&](int t) { return p.window > 0 ? max(0, tile_first(t) - p.window + 1) : 0; };
+    auto first_seen = [&](int pos) {
+        int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+        if (p.chunk > 0) lo = max(lo, pos - pos % p.chunk);
+        return lo;
+    };
+    auto tile_lo = [&](int t) { return first_seen(tile_first(t)); };
     const int kb_first = tile_lo(0) / BKV * BKV;
     const int n_blocks = (pos_last - kb_first) / BKV + 1;
     auto block_first = [&](int t) { return (tile_lo(t) / BKV * BKV - kb_first) / BKV; };
@@ -351,7 +359,7 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         const int r = quarter * 32 + lane;
         const int t_first = tile_first(t), rows = tile_last(t) - t_first + 1;
         const int qpos = t_first + r;
-        const int qlo = p.window > 0 ? max(0, qpos - p.window + 1) : 0;
+        const int qlo = first_seen(qpos);
         const int j_first = block_first(t), j_last = block_last(t);
         const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
         // m: the maximum the row's exponentials, sum and output are relative to. It follows the true running maximum only
@@ -452,7 +460,9 @@ attention_prefill_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, cons
         if (alive) alive = __all_sync(0xffffffffu, tc::mbar_wait(&o_full[t], (j_last - j_first) & 1, abort_flag));
         if (alive) {
             tc::fence_after_sync();
-            const float inv = l > 0.f ? 1.f / l : 0.f;
+            float inv = l > 0.f ? 1.f / l : 0.f;
+            if (p.gate && r < rows)
+                inv *= 1.0f / (1.0f + __expf(-__bfloat162float(p.gate[(size_t)(row0 + t * BQ + r) * p.gate_stride + h])));
             __nv_bfloat16* dst = p.out + (size_t)(row0 + t * BQ + r) * p.out_stride + (size_t)h * D;
 #pragma unroll
             for (int d0 = 0; d0 < D; d0 += 32) {
@@ -531,11 +541,13 @@ DD_API int dd_attention_prefill_tcgen05_supported(int n_heads, int n_kv_heads, i
 // (dd_kv_store's work, done by TMA from the tiles in shared memory). Only for steps in which every entry starts at a
 // position that is a multiple of 128, so that no key block mixes cached and new keys (the caller's duty; an entry
 // that breaks it sets error bit 2 and writes nothing).
+// chunk > 0: a query sees only the keys of its own chunk of that many positions (counted from position 0). gate: null,
+// or rows of gate_stride bf16 with one element per head, whose logistic function multiplies the head's output.
 DD_API int dd_attention_prefill_tcgen05(const void* q, int q_stride, const void* k_new, const void* v_new, int store_new, void* cache, const int* entry_start,
                                         const int* entry_pos0, int n_entries, int n_tokens, const int* block_table,
                                         int max_blocks, void* out, int out_stride, int n_heads, int n_kv_heads,
                                         int head_dim, int page_size, int n_pages, int window, float scale,
-                                        int* error_flag, void* stream) {
+                                        int* error_flag, void* stream, int chunk, const void* gate, int gate_stride) {
     if (n_tokens <= 0 || n_entries <= 0) return 0;
     if (!dd_attention_prefill_tcgen05_supported(n_heads, n_kv_heads, head_dim, page_size, DD_BF16))
         return dd_fail("dd_attention_prefill_tcgen05: needs head size 64, pages of 8 to 128 tokens (a power of two) and heads a "
@@ -567,6 +579,7 @@ DD_API int dd_attention_prefill_tcgen05(const void* q, int q_stride, const void*
     p.out = (__nv_bfloat16*)out; p.error_flag = error_flag;
     p.n_entries = n_entries; p.max_blocks = max_blocks; p.out_stride = out_stride; p.H = n_heads; p.KH = n_kv_heads;
     p.P = page_size; p.n_pages = n_pages; p.window = window; p.scale_log2e = scale * 1.4426950408889634f;
+    p.chunk = chunk; p.gate = (const __nv_bfloat16*)gate; p.gate_stride = gate_stride;
     p.new_rows = k_new != nullptr;
     p.store_new = store_new != 0;
     // an upper bound of the number of pairs of 128-row tiles; blocks beyond the real count return at once

@@ -52,16 +52,16 @@ _SIGNATURES = {
         "dd_attention_decode_supported": [_c_int] * 4,
         "dd_attention_prefill_supported": [_c_int] * 4,
         "dd_attention_prefill": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int]
-                                + [_c_int] * 6 + [_c_float, _c_void, _c_void],
+                                + [_c_int] * 6 + [_c_float, _c_void, _c_void, _c_int, _c_void, _c_int],
         "dd_attention_prefill_tcgen05_supported": [_c_int] * 5,
         "dd_attention_prefill_tcgen05": [_c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_int, _c_void, _c_int, _c_void, _c_int]
-                                        + [_c_int] * 6 + [_c_float, _c_void, _c_void],
+                                        + [_c_int] * 6 + [_c_float, _c_void, _c_void, _c_int, _c_void, _c_int],
         "dd_attention_decode_pages_supported": [_c_int] * 5,
         "dd_attention_decode_pages_splits": [_c_int] * 5,
         "dd_attention_decode_pages": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int,
-                                      _c_void, _c_void, _c_void] + [_c_int] * 7 + [_c_float, _c_int, _c_void, _c_void],
+                                      _c_void, _c_void, _c_void] + [_c_int] * 7 + [_c_float, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int],
         "dd_attention_decode": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int,
-                                _c_void, _c_void, _c_void] + [_c_int] * 7 + [_c_float, _c_int, _c_void, _c_void],
+                                _c_void, _c_void, _c_void] + [_c_int] * 7 + [_c_float, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int],
         "dd_gemm_tcgen05": [_c_void, _c_int, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int] + [_c_int] * 8
                            + [_c_void, _c_void, _c_int, _c_void, ctypes.c_longlong, _c_void, _c_void],
     },
@@ -541,14 +541,22 @@ def attention_decode_pages_splits(n_tokens, n_heads, page_size, context, device)
     return int(library("tensor").dd_attention_decode_pages_splits(n_tokens, n_heads, page_size, context, sm_count(device)))
 
 
+def _gate_args(gate, q, n_heads, chunk):
+    """(chunk, gate pointer, gate row stride) as the attention launchers take them."""
+    if gate is not None and (gate.shape != (q.shape[0], n_heads) or gate.stride(1) != 1 or gate.dtype != q.dtype):
+        raise KernelError("attention: the gate must be a [tokens, heads] row view in q's dtype")
+    return 0 if chunk is None else int(chunk), _ptr(gate, "gate"), 0 if gate is None else gate.stride(0)
+
+
 def attention_decode(q, cache, token_entry, positions, block_table, n_heads, scale, window=None, n_splits=1, out=None,
-                     k_new=None, v_new=None, kernel="rows"):
+                     k_new=None, v_new=None, kernel="rows", chunk=None, gate=None):
     """Decode attention (one query per token) over a bfloat16 cache. kernel 'rows': a warp copies key rows 16 bytes
     at a time (see attention_decode_supported); 'pages': whole pages of a group of heads by TMA (see
     attention_decode_pages_supported). With k_new/v_new (row views of the buffer q lives in) the step's own keys and
     values are used from there and written into the cache by this kernel; otherwise they must be in the cache already.
     token_entry None: token t belongs to entry t (a step of single tokens in entry order). n_splits: into how many
-    pieces a token's keys are cut; for 'pages' the most a token may get (the kernel deals them out by context length)."""
+    pieces a token's keys are cut; for 'pages' the most a token may get (the kernel deals them out by context length).
+    chunk, gate: as attention_rows."""
     if kernel not in ("rows", "pages"):
         raise KernelError(f"attention_decode: unknown kernel {kernel!r}")
     n_pages, _, kv_heads, page_size, head_dim = cache.shape
@@ -573,7 +581,8 @@ def attention_decode(q, cache, token_entry, positions, block_table, n_heads, sca
           _ptr(cache, "cache"), _ptr(token_entry, "token_entry", torch.int32), _ptr(positions, "positions", torch.int32),
           _ptr(block_table, "block_table", torch.int32), block_table.shape[1], _ptr(out, "out"), out.stride(0),
           _ptr(part_o), _ptr(part_ml), _ptr(counters), n, n_heads, kv_heads, head_dim, page_size, n_pages,
-          0 if window is None else int(window), float(scale), int(n_splits), _ptr(error_flag(q.device)), _stream())
+          0 if window is None else int(window), float(scale), int(n_splits), _ptr(error_flag(q.device)), _stream(),
+          *_gate_args(gate, q, n_heads, chunk))
     return out
 
 
@@ -590,7 +599,7 @@ ATTENTION_PREFILL_TCGEN05_KEY_BLOCK = 128       # keys per block of the tcgen05 
 
 
 def attention_prefill(q, cache, entry_start, entry_pos0, block_table, n_heads, scale, window=None, out=None, kernel="mma",
-                      k_new=None, v_new=None, store_new=False):
+                      k_new=None, v_new=None, store_new=False, chunk=None, gate=None):
     """Tensor-core attention for runs of consecutive tokens (prompt portions; a decoded token is a run of one)
     over a bfloat16 cache. entry_start: int32 [E+1], entry_pos0: int32 [E]. kernel: 'mma' (mma.sync tiles of 64
     queries, see attention_prefill_supported) or 'tcgen05' (tiles of 128 queries with TMA and TMEM accumulators,
@@ -598,7 +607,8 @@ def attention_prefill(q, cache, entry_start, entry_pos0, block_table, n_heads, s
     (row views of the buffer q lives in, the same values) let the tcgen05 kernel read the key blocks that lie wholly
     in this step from there, in one piece per block instead of page by page. store_new: the tcgen05 kernel writes
     k_new/v_new into the cache itself (no kv_store before it); only for steps whose entries all start at a position
-    that is a multiple of ATTENTION_PREFILL_TCGEN05_KEY_BLOCK (an entry that does not sets error bit 2)."""
+    that is a multiple of ATTENTION_PREFILL_TCGEN05_KEY_BLOCK (an entry that does not sets error bit 2).
+    chunk, gate: as attention_rows."""
     n_pages, _, kv_heads, page_size, head_dim = cache.shape
     n, n_entries = q.shape[0], entry_pos0.numel()
     if q.shape[1] != n_heads * head_dim or q.stride(1) != 1 or q.dtype != torch.bfloat16 or cache.dtype != torch.bfloat16 \
@@ -621,5 +631,5 @@ def attention_prefill(q, cache, entry_start, entry_pos0, block_table, n_heads, s
           _ptr(entry_start, "entry_start", torch.int32), _ptr(entry_pos0, "entry_pos0", torch.int32), n_entries, n,
           _ptr(block_table, "block_table", torch.int32), block_table.shape[1], _ptr(out, "out"), out.stride(0),
           n_heads, kv_heads, head_dim, page_size, n_pages, 0 if window is None else int(window), float(scale),
-          _ptr(error_flag(q.device)), _stream())
+          _ptr(error_flag(q.device)), _stream(), *_gate_args(gate, q, n_heads, chunk))
     return out

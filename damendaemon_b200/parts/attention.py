@@ -43,6 +43,11 @@ class Attention(Mixer):
     def __init__(self, spec, weights, runtime):
         self.spec, self.runtime = spec, runtime
         self.qkv_w = weights[_projection(spec)[1]]
+        if self.qkv_w.shape[0] % 8:
+            # the attention kernels read the projection's rows in 16-byte pieces: rows of zeros after a gate's few
+            # make the row stride a multiple of eight elements (their outputs are never read)
+            pad = torch.zeros((-self.qkv_w.shape[0] % 8, self.qkv_w.shape[1]), dtype=self.qkv_w.dtype, device=self.qkv_w.device)
+            self.qkv_w = weights[_projection(spec)[1]] = torch.cat([self.qkv_w, pad], dim=0)
         self.qkv_b = weights[_joined(spec.qkv_bias)] if spec.qkv_bias else None
         self.out_w = weights[spec.out_weight]
         self.out_b = weights[spec.out_bias] if spec.out_bias else None
@@ -62,8 +67,7 @@ class Attention(Mixer):
             raise ValueError(f"{spec.n_heads} heads cannot share {spec.n_kv_heads} key/value heads")
         # where this mixer likes a prompt to be cut: the key block of its prompt kernel, if that kernel takes its sizes
         self.portion_multiple = 1
-        if runtime.dtype == torch.bfloat16 and runtime.attention == "auto" and runtime.gemm != "simt" and plain \
-                and not spec.chunk and not spec.gate_weight:
+        if runtime.dtype == torch.bfloat16 and runtime.attention == "auto" and runtime.gemm != "simt" and plain:
             self.portion_multiple = prompt_key_block(spec.n_heads, spec.n_kv_heads, spec.head_dim, runtime.page_size, runtime.dtype)
 
     @staticmethod
@@ -98,7 +102,7 @@ class Attention(Mixer):
         q = qkv[:, :self.q_width]
         k = qkv[:, self.q_width:self.q_width + self.kv_width]
         v = qkv[:, self.q_width + self.kv_width:self.q_width + self.kv_width + self.v_width]
-        gate = qkv[:, self.q_width + self.kv_width + self.v_width:] if s.gate_weight else None
+        gate = qkv[:, self.q_width + self.kv_width + self.v_width:][:, :s.n_heads] if s.gate_weight else None
         q, k = position.on_query_key(q, k, ctx)
         if self.rotary is not None:
             q, k = self.rotary.on_query_key(q, k, ctx)

@@ -59,7 +59,8 @@ def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None, chunk=None
                                       v_dim=value_dim)
     kv_heads, page_size, head_dim = kv.shape[2], kv.shape[3], kv.shape[4]
     k_new, v_new = (k, v) if cache.writable else (None, None)
-    fast = runtime.attention != "rows" and not chunk and gate is None
+    fast = runtime.attention != "rows"
+    masked = dict(chunk=chunk, gate=gate)      # every kernel takes the chunked mask and the gate on its output
     tensor = fast and runtime.attention != "mma"
     def wants_pages(n_tokens):
         pairs = n_tokens * n_heads
@@ -71,12 +72,12 @@ def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None, chunk=None
         splits = max(splits, -(-table.shape[1] // tune.pages_per_block))
         # (decode only: token t is entry t, so the kernels are spared the look-up)
         return kernels.attention_decode(q, kv, None, ctx.positions, table, n_heads, scale, window,
-                                        n_splits=splits, k_new=k_new, v_new=v_new, kernel="pages")
+                                        n_splits=splits, k_new=k_new, v_new=v_new, kernel="pages", **masked)
     if ctx.decode_only and fast and kernels.attention_decode_supported(n_heads, kv_heads, head_dim, q.dtype):
         # the decode kernel takes the new keys and values from the projection and writes them itself
         splits = ctx.key_splits(n_heads, keys_per_block=tune.row_keys_per_block, blocks_per_sm=tune.row_blocks_per_sm)
         return kernels.attention_decode(q, kv, None, ctx.positions, table, n_heads, scale, window,
-                                        n_splits=splits, k_new=k_new, v_new=v_new)
+                                        n_splits=splits, k_new=k_new, v_new=v_new, **masked)
     tcgen05 = not ctx.decode_only and tensor and \
         kernels.attention_prefill_tcgen05_supported(n_heads, kv_heads, head_dim, page_size, q.dtype)
     mma = not tcgen05 and not ctx.decode_only and fast and kernels.attention_prefill_supported(n_heads, kv_heads, head_dim, q.dtype)
@@ -99,7 +100,8 @@ def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None, chunk=None
                                     n_tokens=n1)
         kernels.attention_decode(q[:n1], kv, None, ctx.positions[:n1], table, n_heads, scale, window, n_splits=splits,
                                  out=out[:n1], k_new=None if k_new is None else k_new[:n1],
-                                 v_new=None if v_new is None else v_new[:n1], kernel="pages" if pages else "rows")
+                                 v_new=None if v_new is None else v_new[:n1], kernel="pages" if pages else "rows",
+                                 chunk=chunk, gate=None if gate is None else gate[:n1])
         if n1 == ctx.n_entries:
             return out
     # the tcgen05 prompt kernel writes the cache itself when no key block of its entries mixes cached and new keys
@@ -108,9 +110,9 @@ def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None, chunk=None
         kernels.kv_store(k[n1:], v[n1:], ctx.token_entry[n1:], ctx.positions[n1:], table, kv)
     if tcgen05:
         return kernels.attention_prefill(q, kv, ctx.entry_start[n1:], ctx.entry_pos0[n1:], table[n1:], n_heads, scale, window,
-                                         out=out, kernel="tcgen05", k_new=k_new, v_new=v_new, store_new=fused_store)
+                                         out=out, kernel="tcgen05", k_new=k_new, v_new=v_new, store_new=fused_store, **masked)
     if mma:
         return kernels.attention_prefill(q, kv, ctx.entry_start[n1:], ctx.entry_pos0[n1:], table[n1:], n_heads, scale, window,
-                                         out=out)
+                                         out=out, **masked)
     return kernels.attention_rows(q, kv, ctx.token_entry, ctx.positions, table, n_heads, scale, window,
                                   n_splits=ctx.key_splits(n_heads), chunk=chunk, gate=gate)

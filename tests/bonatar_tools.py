@@ -54,7 +54,12 @@ _RM0 = mixer(2, 1, 64, 64)
 _RM1 = mixer(2, 2, 64, 64, mask=128, rot_dims=32, base=100.0, scaling={"factor": 2.0, "original": 32, "fast": 4.0, "slow": 1.0})
 TINY_R = model(300, 128, [layer(_RM0, moe(3, 3, 32, 2.0, shared=(16, 1.0))), layer(_RM1, dense(128))], eps=1e-6)
 
-CONFIGS = {"P": TINY_P, "Q": TINY_Q, "R": TINY_R}
+# S: heads of 64 with a key/value head each (what every tensor-core attention kernel takes, decode included), chunks of
+# 100 (no multiple of a key block of 128 nor of a page), eight experts of which a token uses two
+_SM = mixer(4, 4, 64, 64, mask=100, rot_dims=64, base=10000.0, scaling={"factor": 8.0, "original": 128, "fast": 16.0, "slow": 1.0})
+TINY_S = model(400, 256, [layer(_SM, moe(8, 2, 64, 3.0, shared=(64, 3.0))), layer(_SM, dense(512)), layer(_SM, dense(512), 1)])
+
+CONFIGS = {"P": TINY_P, "Q": TINY_Q, "R": TINY_R, "S": TINY_S}
 
 
 def make_tensors(config, seed, sharpen=3.0, dtype=torch.float32):

@@ -15,6 +15,15 @@ from pathlib import Path
 import numpy as np
 import torch
 
+# None, or a dtype that stored activations are rounded to (what a 16-bit engine keeps between its kernels), so that a
+# test can measure how far such rounding alone moves the logits of a model
+ROUND = None
+
+
+def kept(x):
+    return x if ROUND is None else x.to(ROUND).to(x.dtype)
+
+
 _NP = {"F32": np.float32, "F64": np.float64, "F16": np.float16, "I32": np.int32, "I64": np.int64}
 
 
@@ -47,7 +56,7 @@ def embed(ids, table, scale):
 
 def rms_norm_offset(x, w, eps):
     """x / sqrt(mean(x^2) + eps) * (1 + w): the weight is stored as its distance from one."""
-    return x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * (1.0 + w)
+    return kept(x / torch.sqrt((x * x).mean(-1, keepdim=True) + eps) * (1.0 + w))
 
 
 def rotary_frequencies(n_rot, base, scaling=None):
@@ -112,31 +121,31 @@ def attention_mixer(h, w, m, positions):
     """The whole mixer on its normed input h [T, D]; w: the mixer's tensors by short name; m: its config."""
     T = h.shape[0]
     H, G, dk, dv = m["heads"], m["kv_heads"], m["dim"], m["vdim"]
-    q = (h @ w["q"].T).view(T, H, dk)
-    k = (h @ w["k"].T).view(T, G, dk)
-    v = (h @ w["v"].T).view(T, G, dv)
+    q = kept(h @ w["q"].T).view(T, H, dk)
+    k = kept(h @ w["k"].T).view(T, G, dk)
+    v = kept(h @ w["v"].T).view(T, G, dv)
     rot = m.get("rot")
     if rot:
         freqs, magnitude = rotary_frequencies(rot["dims"], rot["base"], rot.get("scaling"))
         freqs = freqs.to(h.dtype)
-        q, k = rotate_pairs(q, positions, freqs, magnitude), rotate_pairs(k, positions, freqs, magnitude)
+        q, k = kept(rotate_pairs(q, positions, freqs, magnitude)), kept(rotate_pairs(k, positions, freqs, magnitude))
     mask = m.get("mask")
     out = grouped_attention(q, k, v, m["scale"], visible(T, mask["size"] if mask else None))
-    gate = torch.sigmoid(h @ w["g"].T)                       # [T, H]: one number per head
-    out = out * gate[:, :, None]
+    gate = torch.sigmoid(kept(h @ w["g"].T))                 # [T, H]: one number per head
+    out = kept(out * gate[:, :, None])
     return out.reshape(T, H * dv) @ w["o"].T
 
 
 def dense_ff(h, w):
     """down(relu(up h)^2)."""
-    return torch.relu(h @ w["up"].T) ** 2 @ w["down"].T
+    return kept(torch.relu(h @ w["up"].T) ** 2) @ w["down"].T
 
 
 def clamped_glu_expert(h, w, limit):
     """g = min(gate h, limit), u = clamp(up h, -limit, limit); down(g sigmoid(1.702 g) (u + 1))."""
-    g = (h @ w["gate"].T).clamp(max=limit)
-    u = (h @ w["up"].T).clamp(-limit, limit)
-    return (g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ w["down"].T
+    g = kept(h @ w["gate"].T).clamp(max=limit)
+    u = kept(h @ w["up"].T).clamp(-limit, limit)
+    return kept(g * torch.sigmoid(1.702 * g) * (u + 1.0)) @ w["down"].T
 
 
 def table_routed_experts(h, ids, w, c):

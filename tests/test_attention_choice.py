@@ -34,12 +34,12 @@ class Recorder:
         return 4
 
     def attention_decode(self, q, kv, token_entry, positions, table, n_heads, scale, window, n_splits=1, out=None,
-                         k_new=None, v_new=None, kernel="rows"):
+                         k_new=None, v_new=None, kernel="rows", chunk=None, gate=None):
         self.calls.append(("decode-" + kernel, q.shape[0], token_entry is None, k_new is not None))
         return out if out is not None else q
 
     def attention_prefill(self, q, kv, entry_start, entry_pos0, table, n_heads, scale, window=None, out=None, kernel="mma",
-                          k_new=None, v_new=None, store_new=False):
+                          k_new=None, v_new=None, store_new=False, chunk=None, gate=None):
         self.calls.append(("prefill-" + kernel, entry_pos0.numel(), bool(store_new), table.shape[0]))
         return out if out is not None else q
 
