@@ -91,8 +91,9 @@ def make_runtime(config, batch, use_graph=True, seed=0, dtype="bfloat16"):
     typed = arch.parse_config(config)
     tensors = arch.random_tensors(typed, seed, torch.bfloat16, device="cuda")
     slots = max(batch, 2)           # the prefill of two prompts runs on the same engine
-    runtime = Runtime(None, config=config, tensors=tensors, dtype=dtype, max_batch=slots,
-                      kv_cache_tokens=slots * config["n_positions"], use_graph=use_graph, token_budget=4096)
+    positions = config.get("n_positions") or 1024       # a configuration without a limit of its own gets this context
+    runtime = Runtime(None, positions, config=config, tensors=tensors, dtype=dtype, max_batch=slots,
+                      kv_cache_tokens=slots * positions, use_graph=use_graph, token_budget=4096)
     del tensors
     torch.cuda.empty_cache()
     return runtime
@@ -140,7 +141,7 @@ def decode_device_timed(engine, batch, warmup, steps, vocab, prompt_len=PROMPT):
     ms = start.elapsed_time(stop) / steps
     kv_per_token = engine.cache.bytes_per_token(2)
     contexts = [prompt_len + s + 1 for s in range(warmup, warmup + steps)]
-    position_table = engine.spec.max_positions * engine.spec.width * 2
+    position_table = (engine.spec.max_positions or 0) * engine.spec.width * 2
     bytes_per_step = engine.weight_bytes - position_table + batch * kv_per_token * statistics.mean(contexts)
     for r in prompts:
         engine.finish(r)
@@ -325,6 +326,76 @@ def parity(layers):
             "logit_scale": float(max(v.abs().max() for v in want.values()))}
 
 
+DESIGN_SIZES = {
+    # name: width, heads of 64 (each with keys and values of its own), dense inner width, experts x inner width, experts a token
+    "w1600": dict(width=1600, heads=25, ff=6400, experts=16, expert_ff=1600, top=2),
+    "w2048": dict(width=2048, heads=32, ff=8192, experts=16, expert_ff=2048, top=2),
+}
+DESIGN_KERNEL_PAIRS = [      # (a kernel of the new design, the like kernel of GPT-2) at width 1600, 25 heads of 64
+    ("rmsnorm_m2048", "layernorm_m2048"), ("rmsnorm_m8", "layernorm_m8"),
+    ("attn_prefill_p2_t1024_masked", "attn_prefill_p2_t1024"), ("attn_decode_b8_masked", "attn_decode_b8"),
+    ("attn_decode_rows_b8_masked", "attn_decode_rows_b8"), ("attn_decode_b64_masked", "attn_decode_b64"),
+    ("grouped_up_m2048", "gemm_fc_m2048"), ("grouped_down_m2048", "gemm_fc2_m2048"),
+    ("grouped_up_m8", "gemm_fc_m8"), ("grouped_down_m8", "gemm_fc2_m8"),
+    ("rotary_m2048", None), ("rotary_m8", None), ("grouped_route_m2048", None), ("grouped_route_m8", None),
+]
+
+
+def design_configs(size, layers, vocab=50257):
+    """GPT-2 and two Bonatar models (dense layers only; expert layers only) whose layers have one size."""
+    z = DESIGN_SIZES[size]
+    gpt2 = dict(XL, n_layer=layers, n_embd=z["width"], n_head=z["heads"], n_inner=z["ff"], vocab_size=vocab)
+    mixer = {"heads": z["heads"], "kv_heads": z["heads"], "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": 1024},
+             "rot": {"dims": 64, "base": 10000.0, "scaling": {"factor": 4.0, "original": 256, "fast": 32.0, "slow": 1.0}}}
+    moe = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"]}, "expert": {"ff": z["expert_ff"], "limit": 7.0},
+           "shared": {"ff": z["expert_ff"], "limit": 7.0}}
+
+    def bonatar(mlp):
+        return {"architecture": "Bonatar", "vocab": vocab, "width": z["width"], "embedding": {"scale": z["width"] ** 0.5},
+                "norm": {"eps": 1e-6}, "layers": [{"type": "attention", "mixer": mixer, "mlp": mlp} for _ in range(layers)]}
+    return {"gpt2": gpt2, "bonatar_dense": bonatar({"kind": "dense", "ff": z["ff"]}), "bonatar_experts": bonatar(moe)}
+
+
+def design_bench(args):
+    """``--design bonatar``: prefill and decode throughput of Bonatar beside GPT-2 at equal layer sizes (random
+    bfloat16 weights, a few layers), and each kernel of the new design beside the like kernel of GPT-2, timed in a
+    chain replayed from a CUDA graph over inputs that rotate through more memory than L2 holds."""
+    import torch
+    from bench_kernel_cases import time_case
+    measured_peaks, peaks_from = peaks()
+    hbm, tflops = measured_peaks["hbm_gbs"], measured_peaks["bf16_tflops"]
+    layers = args.layers or 6
+    out = {"design": "bonatar", "layers": layers, "dtype": "bf16", "data": "synthetic", "peaks": dict(measured_peaks, source=peaks_from),
+           "sizes": {}, "kernels": [],
+           "note": "throughput in tokens a second on one B200, timed on the device; chunks of 1024 positions hold the whole context, "
+                   "so both designs attend over the same keys"}
+    for size in DESIGN_SIZES:
+        row = {}
+        for name, config in design_configs(size, layers).items():
+            runtime = make_runtime(config, 8)
+            vocab = runtime.engine.spec.vocab_size
+            ms_prefill = prefill_timed(runtime.engine, vocab)
+            ms, _, launches = decode_device_timed(runtime.engine, 8, max(args.warmup, 3), min(args.steps, 200), vocab)
+            row[name] = {"prefill_2x1024_ms": round(ms_prefill, 3), "prefill_tok_s": round(2048 / ms_prefill * 1e3),
+                         "decode_b8_ms": round(ms, 4), "decode_b8_tok_s": round(8 / ms * 1e3), "launches_per_decode_step": launches,
+                         "weight_GB": round(runtime.engine.weight_bytes / 1e9, 3)}
+            del runtime
+            torch.cuda.empty_cache()
+        out["sizes"][size] = row
+
+    def measured(case):
+        r = time_case(case, args.case_iters, graph=True)
+        r["roofline_fraction"] = round(max(r["GB_per_s"] / hbm, r["TFLOP_per_s"] / tflops), 4)
+        return r
+    for new, like in DESIGN_KERNEL_PAIRS:
+        entry = {"new": measured(new), "like": measured(like) if like else None}
+        if like:
+            entry["fraction_new_over_like"] = round(entry["new"]["roofline_fraction"] / max(entry["like"]["roofline_fraction"], 1e-9), 3)
+        out["kernels"].append(entry)
+    print(json.dumps(out), flush=True)
+    return 0
+
+
 def line_config(layers, batch, cuda_graph=True):
     """What both arms run, in the same words (the `config` of the bench line, flat): every size of the model, the batch,
     the lengths. What only one arm can say of itself (page size, timing method) is under `engine`."""
@@ -375,6 +446,8 @@ def main():
     parser.add_argument("--case-iters", type=int, default=50)
     parser.add_argument("--case-graph", action="store_true", help="time the kernel case as launches replayed from one CUDA graph")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), help="run a scheduler workload instead of the headline bench")
+    parser.add_argument("--design", choices=("bonatar",), help="another design beside GPT-2 at equal layer sizes (prefill, decode, "
+                        "kernel by kernel) instead of the headline bench")
     parser.add_argument("--parity", action="store_true", help="the float32 engine beside the bfloat16 one: on the benchmark's model "
                         "(logit differences, greedy agreement), or with --workload on that workload (the same requests in both)")
     args = parser.parse_args()
@@ -383,6 +456,8 @@ def main():
         return 2
     if args.impl == "reference":
         return reference_arm(args)
+    if args.design:
+        return design_bench(args)
     if args.workload:
         result = run_workload(args.workload)
         if args.parity:

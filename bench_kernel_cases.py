@@ -69,6 +69,65 @@ def _layernorm_case(rows, dev):
     return run, {"bytes": rows * width * 6, "flops": 8 * rows * width}
 
 
+def _rmsnorm_case(rows, dev):
+    """RMS norm (weight stored around zero) of `rows` rows of the float32 stream (width 1600) into bfloat16."""
+    width = H * D
+    copies = max(2, min(24, (300 << 20) // (rows * width * 4)))
+    xs = [torch.randn(rows, width, device=dev) for _ in range(copies)]
+    weight = torch.zeros(width, device=dev)
+    out = torch.empty(rows, width, device=dev, dtype=torch.bfloat16)
+    run = lambda i: K.rmsnorm(xs[i % copies], weight, 1e-6, torch.bfloat16, offset=1.0, out=out)
+    return run, {"bytes": rows * width * 6, "flops": 4 * rows * width}
+
+
+def _rotary_case(rows, dev):
+    """Rotary positions on the queries and keys of `rows` tokens (25 + 25 heads of 64, all dimensions rotated)."""
+    copies = max(2, min(24, (300 << 20) // (rows * 3 * H * D * 2)))
+    bufs = [torch.randn(rows, 3 * H * D + 32, device=dev).to(torch.bfloat16) for _ in range(copies)]
+    pos = torch.arange(rows, dtype=torch.int32, device=dev) % 1024
+    freqs = (10000.0 ** (-torch.arange(D // 2, dtype=torch.float64) * 2 / D)).float().to(dev)
+    run = lambda i: K.rotary(bufs[i % copies][:, :H * D], bufs[i % copies][:, H * D:2 * H * D], pos, freqs, 1.0, H, H, D)
+    return run, {"bytes": rows * 2 * H * D * 4, "flops": 6 * rows * H * D}
+
+
+EXPERTS, TOP, INNER = 16, 2, 1600       # sixteen experts of a quarter of the dense inner width, two per token
+
+
+def _grouped_case(which, tokens, dev):
+    """The experts' products of a step of `tokens` tokens (width 1600): 'up' = gate and up with the gated unit fused,
+    'down' = the down projection into float32 rows; 'route' = sorting the pairs, gathering the rows and the weighted sum."""
+    width = H * D
+    g = torch.Generator().manual_seed(0)
+    table = torch.rand((50257, EXPERTS), generator=g).argsort(dim=1)[:, :TOP].to(torch.int32).contiguous().to(dev)
+    ids = torch.randint(0, 50257, (tokens,), generator=g).to(torch.int32).to(dev)
+    from damendaemon_b200.parts.linear import grouped_tile
+    from damendaemon_b200.parts import Runtime
+    x = torch.randn(tokens, width, device=dev).to(torch.bfloat16)
+    tile = grouped_tile(Runtime(torch.bfloat16, torch.device(dev)), x, tokens * TOP, EXPERTS)
+    pair_row, row_token, tile_group = K.route_by_table(ids, table, EXPERTS, tile)
+    rows = K.gather_rows(x, row_token)
+    used = min(EXPERTS, tokens * TOP)      # experts whose matrices a step streams at least
+    if which == "route":
+        stream = torch.zeros(tokens, width, device=dev)
+        y = torch.zeros(rows.shape[0], width, device=dev)
+
+        def run(i):
+            pr, rt, tg = K.route_by_table(ids, table, EXPERTS, tile)
+            K.gather_rows(x, rt)
+            K.combine_rows(y, pr, stream, TOP, 1.0 / TOP)
+        return run, {"bytes": tokens * TOP * width * (2 + 2 + 4) + tokens * width * 8, "flops": tokens * TOP * width}
+    if which == "up":
+        copies = max(2, min(8, (300 << 20) // (EXPERTS * 2 * INNER * width * 2)))
+        weights = [torch.randn(EXPERTS, 2 * INNER, width, device=dev).mul_(0.02).to(torch.bfloat16) for _ in range(copies)]
+        run = lambda i: K.gemm_grouped_tcgen05(rows, weights[i % copies], tile_group, tile, gated=(7.0, 1.702))
+        return run, {"bytes": used * 2 * INNER * width * 2, "flops": 2 * tokens * TOP * 2 * INNER * width}
+    hidden = torch.randn(rows.shape[0], INNER, device=dev).to(torch.bfloat16)
+    copies = max(2, min(8, (300 << 20) // (EXPERTS * INNER * width * 2)))
+    weights = [torch.randn(EXPERTS, width, INNER, device=dev).mul_(0.02).to(torch.bfloat16) for _ in range(copies)]
+    run = lambda i: K.gemm_grouped_tcgen05(hidden, weights[i % copies], tile_group, tile, out_dtype=torch.float32)
+    return run, {"bytes": used * INNER * width * 2, "flops": 2 * tokens * TOP * INNER * width}
+
+
 def _cache_case(batch, context, dev, copies):
     n_pages = batch * ((context + PAGE - 1) // PAGE)
     caches = [torch.randn(n_pages, 2, H, PAGE, D, device=dev).to(torch.bfloat16) for _ in range(copies)]
@@ -76,7 +135,7 @@ def _cache_case(batch, context, dev, copies):
     return caches, table
 
 
-def _decode_case(batch, context, dev, kernel="pages"):
+def _decode_case(batch, context, dev, kernel="pages", masked=False):
     copies = max(2, min(12, (300 << 20) // (batch * context * H * D * 4)))
     caches, table = _cache_case(batch, context, dev, copies)
     ent = torch.arange(batch, dtype=torch.int32, device=dev)
@@ -86,26 +145,41 @@ def _decode_case(batch, context, dev, kernel="pages"):
         splits = K.attention_decode_pages_splits(batch, H, PAGE, context, dev)
     else:
         splits = max(1, min(-(-(K.sm_count(dev) * 2) // (batch * H)), (context + 127) // 128, 32))
-    run = lambda i: K.attention_decode(q, caches[i % copies], ent, pos, table, H, D ** -0.5, None, n_splits=splits, kernel=kernel)
+    # masked: a chunked mask whose chunk holds the whole context (the same keys are read) and a gate on every head
+    more = dict(chunk=1024 * ((context + 1023) // 1024), gate=torch.randn(batch, H, device=dev).to(torch.bfloat16)) if masked else {}
+    run = lambda i: K.attention_decode(q, caches[i % copies], ent, pos, table, H, D ** -0.5, None, n_splits=splits, kernel=kernel, **more)
     return run, {"bytes": batch * context * H * D * 4, "flops": 4 * batch * context * H * D}
 
 
-def _prefill_case(prompts, length, dev, kernel="tcgen05", store=False):
+def _prefill_case(prompts, length, dev, kernel="tcgen05", store=False, masked=False):
     caches, table = _cache_case(prompts, length, dev, 4)
     start = torch.arange(prompts + 1, dtype=torch.int32, device=dev) * length
     pos0 = torch.zeros(prompts, dtype=torch.int32, device=dev)
     qkv = torch.randn(prompts * length, 3 * H * D, device=dev).to(torch.bfloat16)      # as the fused projection leaves them
     q, k, v = qkv[:, :H * D], qkv[:, H * D:2 * H * D], qkv[:, 2 * H * D:]
     new = {"k_new": k, "v_new": v, "store_new": store} if kernel == "tcgen05" else {}
+    if masked:
+        new.update(chunk=1024 * ((length + 1023) // 1024), gate=torch.randn(prompts * length, H, device=dev).to(torch.bfloat16))
     run = lambda i: K.attention_prefill(q, caches[i % 4], start, pos0, table, H, D ** -0.5, None, kernel=kernel, **new)
     return run, {"bytes": prompts * length * H * D * 6, "flops": prompts * 4 * (length * (length + 1) // 2) * H * D}
 
 
 def build(name, device="cuda:0"):
     """name: gemm_<qkv|proj|fc|fc2|head>_m<tokens> | gemm32_<...>_m<tokens> (float32, CUDA cores) | attn_decode_b<batch>[_c<context>] (page streaming) | attn_decode_rows_b<batch>[_c<context>] | attn_prefill_p<prompts>_t<tokens> | attn_prefill | attn_prefill_store (the kernel writes the cache too) | attn_prefill_mma |
-    attn_prefill_long (one prompt of 4,096 tokens) | layernorm_m<rows>"""
+    attn_prefill_long (one prompt of 4,096 tokens) | layernorm_m<rows> | rmsnorm_m<rows> | rotary_m<rows> |
+    grouped_<up|down|route>_m<tokens> (sixteen experts, two per token); attention cases take the suffix _masked (a chunked
+    mask and a gate on every head's output)"""
     K.library("core"), K.library("tensor")
+    masked = name.endswith("_masked")          # attention cases: with a chunked mask and an output gate
+    if masked:
+        name = name[:-len("_masked")]
     parts = name.split("_")
+    if name.startswith("rmsnorm_m"):
+        return _rmsnorm_case(int(name[len("rmsnorm_m"):]), device)
+    if name.startswith("rotary_m"):
+        return _rotary_case(int(name[len("rotary_m"):]), device)
+    if parts[0] == "grouped" and len(parts) == 3 and parts[1] in ("up", "down", "route") and parts[2][0] == "m":
+        return _grouped_case(parts[1], int(parts[2][1:]), device)
     if parts[0] == "gemm" and len(parts) == 3 and parts[1] in SHAPES and parts[2][0] == "m":
         return _gemm_case(parts[1], int(parts[2][1:]), device)
     if parts[0] == "gemm32" and len(parts) == 3 and parts[1] in SHAPES and parts[2][0] == "m":
@@ -116,11 +190,12 @@ def build(name, device="cuda:0"):
         # attn_decode[_rows]_b<batch>[_c<context>]: the context is 768 keys unless it is given
         rows = name.startswith("attn_decode_rows_b")
         numbers = name[len("attn_decode_rows_b" if rows else "attn_decode_b"):].split("_c")
-        return _decode_case(int(numbers[0]), int(numbers[1]) if len(numbers) > 1 else 768, device, kernel="rows" if rows else "pages")
+        return _decode_case(int(numbers[0]), int(numbers[1]) if len(numbers) > 1 else 768, device, kernel="rows" if rows else "pages",
+                            masked=masked)
     if name.startswith("attn_prefill_p"):
         # attn_prefill_p<prompts>_t<tokens>: whole prompts of that many tokens
         prompts, tokens = name[len("attn_prefill_p"):].split("_t")
-        return _prefill_case(int(prompts), int(tokens), device)
+        return _prefill_case(int(prompts), int(tokens), device, masked=masked)
     if name == "attn_prefill":
         return _prefill_case(2, 1024, device)
     if name == "attn_prefill_store":

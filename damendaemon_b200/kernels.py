@@ -48,6 +48,8 @@ _SIGNATURES = {
     },
     "tensor": {
         "dd_gemm_tcgen05_plan": [_c_int, _c_int, _c_int, _c_int, _c_void, _c_void],
+        "dd_gemm_grouped_tcgen05": [_c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int] + [_c_int] * 5
+                                   + [_c_float, _c_float, _c_int, _c_void, _c_void],
         "dd_wait_probe": [ctypes.c_ulonglong, _c_void, _c_void, _c_void],
         "dd_attention_decode_supported": [_c_int] * 4,
         "dd_attention_prefill_supported": [_c_int] * 4,
@@ -409,6 +411,29 @@ def gemm_simt_grouped(a, w, tile_group, activation=None, out_dtype=None):
     _call(library("core"), "dd_gemm_simt_grouped", _ptr(a, "a"), a.stride(0), _ptr(w, "w"), w.stride(1), w.stride(0),
           _ptr(tile_group, "tile_group", torch.int32), _ptr(out), out.stride(0), M, N, K, ACTIVATIONS[activation],
           _dt(a.dtype), _dt(out_dtype), _stream())
+    return out
+
+
+GROUPED_TCGEN05_TILES = (16, 32, 64, 128)
+
+
+def gemm_grouped_tcgen05(a, w, tile_group, tile, gated=None, out_dtype=None):
+    """a [rows, K] bfloat16 in tiles of ``tile`` rows (one of GROUPED_TCGEN05_TILES); w [groups, N, K] bfloat16; tile i
+    is multiplied with w[tile_group[i]] on the tensor cores (skipped where that is negative). gated=(limit, alpha): w
+    holds gate rows then up rows ([groups, 2 * inner, K]) and the result is the gated unit of the two products,
+    [rows, inner], computed in float32 in the product's epilogue."""
+    _rows(a, "a")
+    if w.dim() != 3 or not w.is_contiguous() or w.shape[2] != a.shape[1] or w.dtype != torch.bfloat16 or a.dtype != torch.bfloat16:
+        raise KernelError(f"grouped gemm: a {tuple(a.shape)} {a.dtype} does not fit w {tuple(w.shape)} {w.dtype}")
+    rows, K = a.shape
+    groups, per_group = w.shape[0], w.shape[1]
+    N = per_group // 2 if gated else per_group
+    out_dtype = out_dtype or torch.bfloat16
+    out = torch.empty((rows, N), dtype=out_dtype, device=a.device)
+    limit, alpha = gated if gated else (0.0, 0.0)
+    _call(library("tensor"), "dd_gemm_grouped_tcgen05", _ptr(a, "a"), a.stride(0), _ptr(w, "w"), w.stride(1), groups, per_group,
+          _ptr(tile_group, "tile_group", torch.int32), _ptr(out), out.stride(0), rows, N, K, int(tile), 1 if gated else 0,
+          float(limit), float(alpha), _dt(out_dtype), _ptr(error_flag(a.device)), _stream())
     return out
 
 

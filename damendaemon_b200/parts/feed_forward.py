@@ -9,7 +9,7 @@ import torch
 
 from .. import kernels
 from .interfaces import FeedForward
-from .linear import grouped_linear, grouped_tile, linear
+from .linear import grouped_gated_unit, grouped_linear, grouped_tile, linear
 from .registry import register_feed_forward
 from .spec import TensorDecl
 
@@ -110,10 +110,9 @@ class TableRoutedExperts(FeedForward):
             gate_up = linear(rt, y, self.shared[0])
             hidden = kernels.gated_unit(gate_up, s.shared.limit, s.shared.alpha)
             residual = linear(rt, hidden, self.shared[1], residual=residual, out_dtype=residual.dtype, out=residual)
-        tile = grouped_tile(rt, y)
+        tile = grouped_tile(rt, y, y.shape[0] * s.top, len(s.experts))
         pair_row, row_token, tile_group = kernels.route_by_table(ctx.token_ids, self.table, len(s.experts), tile)
         rows = kernels.gather_rows(y, row_token)
-        gate_up = grouped_linear(rt, rows, self.gate_up, tile_group, tile)
-        hidden = kernels.gated_unit(gate_up, unit.limit, unit.alpha)
+        hidden = grouped_gated_unit(rt, rows, self.gate_up, tile_group, tile, unit.limit, unit.alpha)
         out = grouped_linear(rt, hidden, self.down, tile_group, tile, out_dtype=torch.float32)
         return kernels.combine_rows(out, pair_row, residual, s.top, 1.0 / s.top)

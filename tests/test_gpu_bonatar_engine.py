@@ -149,10 +149,10 @@ def test_greedy_generation_through_the_scheduler(models, name):
         return ids[len(prompt):]
     want = [greedy(p, 12) for p in prompts]
     for graph in (False, True):
-        runtime = Runtime(None, 256, config=config, tensors=tensors, dtype="float32", max_batch=4, page_size=16, use_graph=graph)
+        runtime = Runtime(None, 512, config=config, tensors=tensors, dtype="float32", max_batch=4, page_size=16, use_graph=graph)
         assert runtime.generate_batch(prompts, 12, ignore_eos=True) == want
         assert runtime.engine.cache.used_tokens == 0
-    runtime = Runtime(None, 256, config=config, tensors=models[name, "bfloat16"][1], dtype="bfloat16", max_batch=4)
+    runtime = Runtime(None, 512, config=config, tensors=models[name, "bfloat16"][1], dtype="bfloat16", max_batch=4)
     got = runtime.generate_batch(prompts, 12, ignore_eos=True)
     for p, g, w in zip(prompts, got, want):
         if g != w:   # rounding may flip a near-tie; then the plain logits at the flip must be a near-tie
@@ -203,7 +203,8 @@ def test_the_replay_program_reads_this_architecture(models, tmp_path):
 @pytest.mark.parametrize("name", ["R", "S"])
 def test_the_tensor_core_attention_kernels_mask_and_gate_like_the_general_one(models, name):
     """Heads of 64 in bfloat16 go to the tensor-core kernels (prompt portions; single tokens too where every head has
-    its own keys): the same steps with the general kernel forced give the same rows, to bfloat16's last bits."""
+    its own keys): the same steps with the general kernel forced give the same rows, within what bfloat16 rounding moves
+    them (the tensor-core kernels round the softmax weights to bfloat16 before they meet the values)."""
     from damendaemon_b200 import kernels
     config, tensors, requests, want = models[name, "bfloat16"]
     builder, peak = mixed_steps(requests, seed=5, max_live=4)
@@ -219,6 +220,6 @@ def test_the_tensor_core_attention_kernels_mask_and_gate_like_the_general_one(mo
     for fast, general in zip(rows[False], rows[True]):
         for r in fast:
             for p in fast[r]:
-                assert (fast[r][p] - general[r][p]).square().mean().sqrt().item() < 0.03, (r, p)
+                assert (fast[r][p] - general[r][p]).square().mean().sqrt().item() < abs(TOL[name, "bfloat16"]), (r, p)
     # the fast path fuses the cache write into its attention kernels and splits no keys: it launches fewer kernels
     assert sum(rows["launches", False]) < sum(rows["launches", True])
