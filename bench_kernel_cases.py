@@ -101,12 +101,11 @@ def _grouped_case(which, tokens, dev):
     table = torch.rand((50257, EXPERTS), generator=g).argsort(dim=1)[:, :TOP].to(torch.int32).contiguous().to(dev)
     ids = torch.randint(0, 50257, (tokens,), generator=g).to(torch.int32).to(dev)
     from damendaemon_b200.parts.linear import grouped_tile
-    from damendaemon_b200.parts import Runtime
     x = torch.randn(tokens, width, device=dev).to(torch.bfloat16)
-    tile = grouped_tile(Runtime(torch.bfloat16, torch.device(dev)), x, tokens * TOP, EXPERTS)
+    tile = grouped_tile(True, tokens * TOP, EXPERTS)
     pair_row, row_token, tile_group = K.route_by_table(ids, table, EXPERTS, tile)
     rows = K.gather_rows(x, row_token)
-    used = min(EXPERTS, tokens * TOP)      # experts whose matrices a step streams at least
+    used = int(torch.unique(tile_group[tile_group >= 0]).numel())      # experts whose matrices this step streams
     if which == "route":
         stream = torch.zeros(tokens, width, device=dev)
         y = torch.zeros(rows.shape[0], width, device=dev)

@@ -38,7 +38,9 @@ template <int T, bool DUAL> struct GroupedConfig {
     static constexpr int W_BYTES = DUAL ? 2 * A_BYTES : A_BYTES;
     static constexpr int X_BYTES = T * BK * 2;
     static constexpr int STAGE_BYTES = W_BYTES + X_BYTES;
-    static constexpr int FIT = 200 * 1024 / STAGE_BYTES;
+    // Two blocks share an SM (110 KB of stages each; their accumulators fit tensor memory side by side): a block owns
+    // one tile, so the loads of one run under the products of the other and one's epilogue under the other's products.
+    static constexpr int FIT = 110 * 1024 / STAGE_BYTES;
     static constexpr int STAGES = FIT < 8 ? FIT : 8;
     static constexpr int WANTED = DUAL ? 2 * T : T;
     static constexpr int TMEM_COLS = WANTED < 32 ? 32 : WANTED;          // T is a power of two: so is this
@@ -46,7 +48,7 @@ template <int T, bool DUAL> struct GroupedConfig {
 };
 
 template <int T, bool DUAL>
-__global__ void __launch_bounds__(THREADS, 1)
+__global__ void __launch_bounds__(THREADS, 2)
 gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                     const GroupedParams p) {
     using C = GroupedConfig<T, DUAL>;

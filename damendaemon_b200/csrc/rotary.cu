@@ -4,13 +4,15 @@
 // (2i, 2i + 1) in the interleaved layout and (i, i + n_pairs) in the layout of halves. At position p the pair (a, b)
 // becomes (a c - b s, b c + a s) with c = magnitude * cos(p f_i), s = magnitude * sin(p f_i). The frequencies f_i
 // are a float32 table of the caller's (plain, or blended for a longer context), so any scaling rule is the host's.
-// Position, angle, cosine, sine and the rotation are float32 whatever the storage type; cosf and sinf are the
-// exact functions (an angle reaches thousands of radians).
+// Position, angle, cosine, sine and the rotation are float32 whatever the storage type; sincosf is the
+// exact function (an angle reaches thousands of radians).
 #include "common.cuh"
 
 namespace {
+constexpr int THREADS = 256, PER = 4;      // pairs a thread has in flight at once
+
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(THREADS)
 rotary_kernel(T* __restrict__ q, T* __restrict__ k, int stride, const int* __restrict__ positions,
               const float* __restrict__ freqs, float magnitude, int q_heads, int k_heads, int head_dim, int n_pairs,
               int interleaved) {
@@ -18,23 +20,41 @@ rotary_kernel(T* __restrict__ q, T* __restrict__ k, int stride, const int* __res
     dd_launch_dependents();
     const int t = blockIdx.x;
     const float p = (float)positions[t];          // positions are the step's input, not the projection's output
-    for (int i = threadIdx.x; i < n_pairs; i += blockDim.x) {
-        const float a = p * freqs[i];
-        cs[i] = cosf(a) * magnitude;
-        cs[n_pairs + i] = sinf(a) * magnitude;
+    for (int i = threadIdx.x; i < n_pairs; i += THREADS) {
+        float sn, c;
+        sincosf(p * freqs[i], &sn, &c);
+        cs[i] = c * magnitude;
+        cs[n_pairs + i] = sn * magnitude;
     }
     __syncthreads();
     dd_grid_wait();
     const int items = (q_heads + k_heads) * n_pairs;
-    for (int item = threadIdx.x; item < items; item += blockDim.x) {
-        const int h = item / n_pairs, i = item - h * n_pairs;
-        T* row = h < q_heads ? q + (size_t)t * stride + (size_t)h * head_dim
-                             : k + (size_t)t * stride + (size_t)(h - q_heads) * head_dim;
-        const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + n_pairs;
-        const float a = dd_to_f32(row[ia]), b = dd_to_f32(row[ib]);
-        const float c = cs[i], s = cs[n_pairs + i];
-        row[ia] = dd_from_f32<T>(a * c - b * s);
-        row[ib] = dd_from_f32<T>(b * c + a * s);
+    T* q_row = q + (size_t)t * stride;
+    T* k_row = k + (size_t)t * stride;
+    // A thread reads PER pairs, then rotates and writes them: the loads of a pass are in flight together (one pair
+    // at a time, each pass of the loop cost a trip to memory: 5.8 us for eight tokens).
+    for (int base = 0; base < items; base += THREADS * PER) {
+        float a[PER], b[PER];
+        T* at[PER];
+        int pair[PER];
+#pragma unroll
+        for (int u = 0; u < PER; ++u) {
+            const int item = base + u * THREADS + threadIdx.x;
+            const bool live = item < items;
+            const int h = live ? item / n_pairs : 0;
+            pair[u] = live ? item - h * n_pairs : -1;
+            T* head = h < q_heads ? q_row + (size_t)h * head_dim : k_row + (size_t)(h - q_heads) * head_dim;
+            at[u] = head + (interleaved ? 2 * max(pair[u], 0) : max(pair[u], 0));
+            a[u] = live ? dd_to_f32(at[u][0]) : 0.f;
+            b[u] = live ? dd_to_f32(at[u][interleaved ? 1 : n_pairs]) : 0.f;
+        }
+#pragma unroll
+        for (int u = 0; u < PER; ++u) {
+            if (pair[u] < 0) continue;
+            const float c = cs[pair[u]], sn = cs[n_pairs + pair[u]];
+            at[u][0] = dd_from_f32<T>(a[u] * c - b[u] * sn);
+            at[u][interleaved ? 1 : n_pairs] = dd_from_f32<T>(b[u] * c + a[u] * sn);
+        }
     }
 }
 }  // namespace
@@ -49,10 +69,10 @@ DD_API int dd_rotary(void* q, void* k, int stride, const int* positions, const f
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = 2 * (size_t)n_pairs * sizeof(float);
     if (dtype == DD_F32)
-        dd_launch(rotary_kernel<float>, dim3(n_tokens), dim3(128), smem, s, (float*)q, (float*)k, stride, positions, freqs,
+        dd_launch(rotary_kernel<float>, dim3(n_tokens), dim3(THREADS), smem, s, (float*)q, (float*)k, stride, positions, freqs,
                   magnitude, q_heads, k_heads, head_dim, n_pairs, interleaved);
     else if (dtype == DD_BF16)
-        dd_launch(rotary_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), smem, s, (__nv_bfloat16*)q, (__nv_bfloat16*)k,
+        dd_launch(rotary_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(THREADS), smem, s, (__nv_bfloat16*)q, (__nv_bfloat16*)k,
                   stride, positions, freqs, magnitude, q_heads, k_heads, head_dim, n_pairs, interleaved);
     else
         return dd_fail("dd_rotary: unknown dtype %d", dtype);

@@ -56,8 +56,8 @@ class Attention(Mixer):
         self.kv_width = spec.n_kv_heads * spec.head_dim
         self.v_width = spec.n_kv_heads * self.value_dim
         plain = self.value_dim == spec.head_dim
-        if spec.head_dim > 256 or self.value_dim > 256 or (plain and spec.head_dim % 8):
-            raise ValueError(f"head size {spec.head_dim} is not supported (multiples of 8 up to 256)")
+        if spec.head_dim > 256 or self.value_dim > 256:
+            raise ValueError(f"head sizes {spec.head_dim} and {self.value_dim} are not supported (at most 256)")
         if spec.gate_weight and spec.qkv_bias:
             raise ValueError("a gated attention with projection biases is not supported")
         self.rotary = None if spec.rotary is None else lookup(POSITIONS, spec.rotary, "position encoding")(spec.rotary, weights, runtime)

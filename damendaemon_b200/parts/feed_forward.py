@@ -9,7 +9,7 @@ import torch
 
 from .. import kernels
 from .interfaces import FeedForward
-from .linear import grouped_gated_unit, grouped_linear, grouped_tile, linear
+from .linear import grouped_gated_unit, grouped_linear, grouped_on_tensor_cores, grouped_tile, linear
 from .registry import register_feed_forward
 from .spec import TensorDecl
 
@@ -82,6 +82,7 @@ class TableRoutedExperts(FeedForward):
         if not 0 < spec.top <= len(spec.experts):
             raise ValueError(f"{spec.top} experts per token of {len(spec.experts)}")
         self.table = weights[spec.table]
+        self.tensor_cores = grouped_on_tensor_cores(runtime, runtime.dtype, spec.width, first.inner)
         self.gate_up = torch.stack([torch.cat([weights[u.gate_weight], weights[u.up_weight]], dim=0) for u in spec.experts])
         self.down = torch.stack([weights[u.down_weight] for u in spec.experts])
         # the stacks take the place of the single matrices (one copy on the device, and in the engine's count of bytes)
@@ -110,9 +111,9 @@ class TableRoutedExperts(FeedForward):
             gate_up = linear(rt, y, self.shared[0])
             hidden = kernels.gated_unit(gate_up, s.shared.limit, s.shared.alpha)
             residual = linear(rt, hidden, self.shared[1], residual=residual, out_dtype=residual.dtype, out=residual)
-        tile = grouped_tile(rt, y, y.shape[0] * s.top, len(s.experts))
+        tile = grouped_tile(self.tensor_cores, y.shape[0] * s.top, len(s.experts))
         pair_row, row_token, tile_group = kernels.route_by_table(ctx.token_ids, self.table, len(s.experts), tile)
         rows = kernels.gather_rows(y, row_token)
-        hidden = grouped_gated_unit(rt, rows, self.gate_up, tile_group, tile, unit.limit, unit.alpha)
-        out = grouped_linear(rt, hidden, self.down, tile_group, tile, out_dtype=torch.float32)
+        hidden = grouped_gated_unit(self.tensor_cores, rows, self.gate_up, tile_group, tile, unit.limit, unit.alpha)
+        out = grouped_linear(self.tensor_cores, hidden, self.down, tile_group, tile, out_dtype=torch.float32)
         return kernels.combine_rows(out, pair_row, residual, s.top, 1.0 / s.top)

@@ -18,31 +18,33 @@ def linear(runtime, a, w, bias=None, residual=None, activation=None, out_dtype=N
     return kernels.gemm_tcgen05(a, w, bias, residual, activation, out_dtype, out)
 
 
-def _grouped_on_tensor_cores(runtime, a):
-    return a.dtype == torch.bfloat16 and runtime.gemm != "simt" and a.shape[1] % 8 == 0 and a.stride(0) % 8 == 0
+def grouped_on_tensor_cores(runtime, dtype, *reductions):
+    """Whether grouped products over these reduction widths run on the tensor cores: bfloat16, and every width a
+    multiple of 8 (TMA needs 16-byte rows). One answer for all products of a part: they share the rows' tiles."""
+    return dtype == torch.bfloat16 and runtime.gemm != "simt" and all(k % 8 == 0 for k in reductions)
 
 
-def grouped_tile(runtime, a, pairs, groups):
-    """Rows per tile of the grouped products that ``grouped_linear`` will run for rows like a: every group's rows start
-    on a multiple of it. The tensor-core kernel takes 16 to 128: about twice the rows a group gets on average, so that
-    few tiles are mostly padding and few groups need several. The CUDA-core kernel has one tile size."""
-    if not _grouped_on_tensor_cores(runtime, a):
+def grouped_tile(tensor_cores, pairs, groups):
+    """Rows per tile of the grouped products: every group's rows start on a multiple of it. The tensor-core kernel
+    takes 16 to 128: about twice the rows a group gets on average, so that few tiles are mostly padding and few groups
+    need several. The CUDA-core kernel has one tile size."""
+    if not tensor_cores:
         return kernels.simt_group_tile()
     want = 2 * pairs // max(1, groups)
     return next((t for t in kernels.GROUPED_TCGEN05_TILES if t >= want), kernels.GROUPED_TCGEN05_TILES[-1])
 
 
-def grouped_linear(runtime, a, w, tile_group, tile, out_dtype=None):
+def grouped_linear(tensor_cores, a, w, tile_group, tile, out_dtype=None):
     """Rows of a in tiles of ``tile``; tile i is multiplied with w[tile_group[i]] (w: [groups, out, in]); tiles whose
     group is negative are skipped."""
-    if _grouped_on_tensor_cores(runtime, a) and w.shape[2] % 8 == 0:
+    if tensor_cores:
         return kernels.gemm_grouped_tcgen05(a, w, tile_group, tile, out_dtype=out_dtype or a.dtype)
     return kernels.gemm_simt_grouped(a, w, tile_group, out_dtype=out_dtype or a.dtype)
 
 
-def grouped_gated_unit(runtime, a, gate_up, tile_group, tile, limit, alpha):
+def grouped_gated_unit(tensor_cores, a, gate_up, tile_group, tile, limit, alpha):
     """The gated unit over grouped rows: gate_up [groups, 2 * inner, in] holds a group's gate rows, then its up rows.
     On the tensor cores both products and the unit are one kernel; else a grouped product and the unit's own kernel."""
-    if _grouped_on_tensor_cores(runtime, a):
+    if tensor_cores:
         return kernels.gemm_grouped_tcgen05(a, gate_up, tile_group, tile, gated=(limit, alpha))
     return kernels.gated_unit(kernels.gemm_simt_grouped(a, gate_up, tile_group), limit, alpha)

@@ -59,7 +59,12 @@ TINY_R = model(300, 128, [layer(_RM0, moe(3, 3, 32, 2.0, shared=(16, 1.0))), lay
 _SM = mixer(4, 4, 64, 64, mask=100, rot_dims=64, base=10000.0, scaling={"factor": 8.0, "original": 128, "fast": 16.0, "slow": 1.0})
 TINY_S = model(400, 256, [layer(_SM, moe(8, 2, 64, 3.0, shared=(64, 3.0))), layer(_SM, dense(512)), layer(_SM, dense(512), 1)])
 
-CONFIGS = {"P": TINY_P, "Q": TINY_Q, "R": TINY_R, "S": TINY_S}
+# T: awkward sizes: a width (100), head sizes (20 and 12), an expert width (30) and a vocabulary (131) that are no
+# multiples of 8, five rotated pairs, three heads on one key/value head, chunks of 33
+_TM = mixer(3, 1, 20, 12, mask=33, rot_dims=10, base=77.0, scaling={"factor": 1.5, "original": 40, "fast": 4.0, "slow": 1.0})
+TINY_T = model(131, 100, [layer(_TM, moe(5, 2, 30, 1.0, shared=(12, 0.5))), layer(_TM, dense(52))], scale=2.5)
+
+CONFIGS = {"P": TINY_P, "Q": TINY_Q, "R": TINY_R, "S": TINY_S, "T": TINY_T}
 
 
 def make_tensors(config, seed, sharpen=3.0, dtype=torch.float32):

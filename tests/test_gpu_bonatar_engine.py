@@ -10,7 +10,7 @@ from trace_tools import mixed_steps, portion_steps, tail_steps, whole_steps
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"P": [1, 5, 23, 24, 25, 49, 100, 130], "Q": [2, 6, 7, 8, 15, 50, 64, 90], "R": [1, 17, 127, 128, 129, 200, 64, 300],
-           "S": [1, 99, 100, 101, 128, 260, 300, 201]}
+           "S": [1, 99, 100, 101, 128, 260, 300, 201], "T": [1, 32, 33, 34, 67, 150, 9, 99]}
 FLOAT32_TOL = 2e-4
 TOL = {}
 
