@@ -223,3 +223,26 @@ def test_the_tensor_core_attention_kernels_mask_and_gate_like_the_general_one(mo
                 assert (fast[r][p] - general[r][p]).square().mean().sqrt().item() < abs(TOL[name, "bfloat16"]), (r, p)
     # the fast path fuses the cache write into its attention kernels and splits no keys: it launches fewer kernels
     assert sum(rows["launches", False]) < sum(rows["launches", True])
+
+
+def test_the_command_line_makes_and_runs_a_model_of_this_architecture(tmp_path):
+    """init-random writes a folder from the architecture's own config.json; run generates from it, greedy tokens equal
+    to the plain implementation reading the same folder."""
+    import json
+    import subprocess
+    import sys
+    from trace_tools import ROOT
+    cfg = tmp_path / "c.json"
+    cfg.write_text(json.dumps(CONFIGS["P"]))
+    made = subprocess.run([sys.executable, "-m", "damendaemon_b200", "init-random", str(cfg), str(tmp_path / "m"), "--seed", "4",
+                           "--dtype", "float32"], capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert made.returncode == 0 and (tmp_path / "m" / "model.safetensors").is_file(), made.stderr[-2000:]
+    out = subprocess.run([sys.executable, "-m", "damendaemon_b200", "run", str(tmp_path / "m"), "--prompt-ids", "3,1,4,1,5,9,2,6",
+                          "--max-tokens", "6", "--dtype", "float32", "--ignore-eos", "--context", "64"],
+                         capture_output=True, text=True, cwd=ROOT, timeout=600)
+    assert out.returncode == 0, out.stderr[-2000:]
+    config, tensors = plain.read_folder(tmp_path / "m")
+    ids = [3, 1, 4, 1, 5, 9, 2, 6]
+    for _ in range(6):
+        ids.append(int(plain.forward(config, tensors, ids)[-1].argmax()))
+    assert [int(t) for t in out.stdout.split()] == ids[8:]

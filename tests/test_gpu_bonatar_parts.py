@@ -38,16 +38,17 @@ def test_embedding_scale():
     assert torch.equal(got, plain.embed(ids.long(), table, 5.25))
 
 
+@pytest.mark.parametrize("pad", [5, 6])       # odd row stride: element by element; even: a pair is one word
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("dim,dims,scaling", [(48, 48, None), (32, 16, {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 2.0}),
                                               (64, 24, {"factor": 2.0, "original": 2048, "fast": 32.0, "slow": 1.0})])
-def test_rotary_pairs_of_neighbours_on_part_of_a_head(dim, dims, scaling, dtype):
+def test_rotary_pairs_of_neighbours_on_part_of_a_head(dim, dims, scaling, dtype, pad):
     from damendaemon_b200 import kernels
     from damendaemon_b200.parts.positions import rotary_frequencies
     from damendaemon_b200.parts.spec import LongContextBlend, RotarySpec
     H, G, T = 3, 2, 11
     positions = torch.tensor([0, 1, 2, 63, 64, 65, 1000, 2047, 2048, 5000, 7], dtype=torch.int32)
-    buf = rnd(T, (H + G) * dim + 5, seed=4).to(dtype)
+    buf = rnd(T, (H + G) * dim + pad, seed=4).to(dtype)
     want_f, want_m = plain.rotary_frequencies(dims, 10000.0, scaling)
     spec = RotarySpec("rotary", dim, dims, 10000.0, True, None if scaling is None else LongContextBlend(**scaling))
     freqs, magnitude = rotary_frequencies(spec)
