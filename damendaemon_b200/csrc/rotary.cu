@@ -29,7 +29,9 @@ template <> struct Pair<__nv_bfloat16> {
     }
 };
 
-template <typename T>
+// WORDS: neighbours are paired and every pair is an aligned word (decided by the launcher), so no branch stands
+// between the loads of a pass.
+template <typename T, bool WORDS>
 __global__ void __launch_bounds__(THREADS)
 rotary_kernel(T* __restrict__ q, T* __restrict__ k, int stride, const int* __restrict__ positions,
               const float* __restrict__ freqs, float magnitude, int q_heads, int k_heads, int head_dim, int n_pairs,
@@ -49,8 +51,6 @@ rotary_kernel(T* __restrict__ q, T* __restrict__ k, int stride, const int* __res
     const int items = (q_heads + k_heads) * n_pairs;
     T* q_row = q + (size_t)t * stride;
     T* k_row = k + (size_t)t * stride;
-    // neighbours as one word: when every pair starts on an even element of a row that starts on a whole word
-    const bool words = interleaved && !(stride & 1) && !(head_dim & 1) && !(((uintptr_t)q | (uintptr_t)k) & (2 * sizeof(T) - 1));
     // A thread reads PER pairs, then rotates and writes them: the loads of a pass are in flight together (one pair
     // at a time, each pass of the loop cost a trip to memory: 5.8 us for eight tokens).
     for (int base = 0; base < items; base += THREADS * PER) {
@@ -66,8 +66,9 @@ rotary_kernel(T* __restrict__ q, T* __restrict__ k, int stride, const int* __res
             T* head = h < q_heads ? q_row + (size_t)h * head_dim : k_row + (size_t)(h - q_heads) * head_dim;
             at[u] = head + (interleaved ? 2 * max(pair[u], 0) : max(pair[u], 0));
             a[u] = b[u] = 0.f;
-            if (live && words) Pair<T>::load(at[u], a[u], b[u]);
-            else if (live) {
+            if (WORDS) {
+                if (live) Pair<T>::load(at[u], a[u], b[u]);
+            } else if (live) {
                 a[u] = dd_to_f32(at[u][0]);
                 b[u] = dd_to_f32(at[u][interleaved ? 1 : n_pairs]);
             }
@@ -76,7 +77,7 @@ rotary_kernel(T* __restrict__ q, T* __restrict__ k, int stride, const int* __res
         for (int u = 0; u < PER; ++u) {
             if (pair[u] < 0) continue;
             const float c = cs[pair[u]], sn = cs[n_pairs + pair[u]];
-            if (words) {
+            if (WORDS) {
                 Pair<T>::store(at[u], a[u] * c - b[u] * sn, b[u] * c + a[u] * sn);
                 continue;
             }
@@ -96,13 +97,20 @@ DD_API int dd_rotary(void* q, void* k, int stride, const int* positions, const f
     if (2 * n_pairs > head_dim) return dd_fail("dd_rotary: %d pairs do not fit a head of %d", n_pairs, head_dim);
     cudaStream_t s = (cudaStream_t)stream;
     const size_t smem = 2 * (size_t)n_pairs * sizeof(float);
-    if (dtype == DD_F32)
-        dd_launch(rotary_kernel<float>, dim3(n_tokens), dim3(THREADS), smem, s, (float*)q, (float*)k, stride, positions, freqs,
-                  magnitude, q_heads, k_heads, head_dim, n_pairs, interleaved);
-    else if (dtype == DD_BF16)
-        dd_launch(rotary_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(THREADS), smem, s, (__nv_bfloat16*)q, (__nv_bfloat16*)k,
-                  stride, positions, freqs, magnitude, q_heads, k_heads, head_dim, n_pairs, interleaved);
-    else
-        return dd_fail("dd_rotary: unknown dtype %d", dtype);
+    if (dtype != DD_F32 && dtype != DD_BF16) return dd_fail("dd_rotary: unknown dtype %d", dtype);
+    // neighbours as one word: when every pair starts on an even element of a row that starts on a whole word
+    const size_t word = dtype == DD_F32 ? 8 : 4;
+    const bool words = interleaved && !(stride & 1) && !(head_dim & 1) && !(((uintptr_t)q | (uintptr_t)k) & (word - 1));
+#define DD_ROTARY(T, W)                                                                                                  \
+    dd_launch(rotary_kernel<T, W>, dim3(n_tokens), dim3(THREADS), smem, s, (T*)q, (T*)k, stride, positions, freqs, magnitude, \
+              q_heads, k_heads, head_dim, n_pairs, interleaved)
+    if (dtype == DD_F32) {
+        if (words) DD_ROTARY(float, true);
+        else DD_ROTARY(float, false);
+    } else {
+        if (words) DD_ROTARY(__nv_bfloat16, true);
+        else DD_ROTARY(__nv_bfloat16, false);
+    }
+#undef DD_ROTARY
     return dd_check_launch("dd_rotary");
 }
