@@ -15,7 +15,7 @@ def rnd(*shape, seed=0, scale=1.0):
     return torch.randn(*shape, generator=g) * scale
 
 
-@pytest.mark.parametrize("width", [48, 320, 2052, 4100])
+@pytest.mark.parametrize("width", [48, 328, 2052, 4100])
 def test_rms_norm_with_a_weight_stored_around_zero(width):
     from damendaemon_b200 import kernels
     x, w = rnd(9, width, seed=1, scale=7.0), rnd(width, seed=2, scale=0.3)
@@ -40,8 +40,8 @@ def test_embedding_scale():
 
 @pytest.mark.parametrize("pad", [5, 6])       # odd row stride: element by element; even: a pair is one word
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("dim,dims,scaling", [(48, 48, None), (32, 16, {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 2.0}),
-                                              (64, 24, {"factor": 2.0, "original": 2048, "fast": 32.0, "slow": 1.0})])
+@pytest.mark.parametrize("dim,dims,scaling", [(40, 40, None), (32, 16, {"factor": 4.0, "original": 64, "fast": 8.0, "slow": 2.0}),
+                                              (64, 24, {"factor": 3.0, "original": 1024, "fast": 16.0, "slow": 2.0})])
 def test_rotary_pairs_of_neighbours_on_part_of_a_head(dim, dims, scaling, dtype, pad):
     from damendaemon_b200 import kernels
     from damendaemon_b200.parts.positions import rotary_frequencies
@@ -49,12 +49,12 @@ def test_rotary_pairs_of_neighbours_on_part_of_a_head(dim, dims, scaling, dtype,
     H, G, T = 3, 2, 11
     positions = torch.tensor([0, 1, 2, 63, 64, 65, 1000, 2047, 2048, 5000, 7], dtype=torch.int32)
     buf = rnd(T, (H + G) * dim + pad, seed=4).to(dtype)
-    want_f, want_m = plain.rotary_frequencies(dims, 10000.0, scaling)
-    spec = RotarySpec("rotary", dim, dims, 10000.0, True, None if scaling is None else LongContextBlend(**scaling))
+    want_f, want_m = plain.rotary_frequencies(dims, 5000.0, scaling)
+    spec = RotarySpec("rotary", dim, dims, 5000.0, True, None if scaling is None else LongContextBlend(**scaling))
     freqs, magnitude = rotary_frequencies(spec)
     assert torch.allclose(freqs, want_f, rtol=1e-12) and magnitude == pytest.approx(want_m)
     if scaling is not None:
-        plain_f = plain.rotary_frequencies(dims, 10000.0)[0]
+        plain_f = plain.rotary_frequencies(dims, 5000.0)[0]
         assert (freqs[0] == plain_f[0]) and freqs[-1] == pytest.approx(plain_f[-1] / scaling["factor"])   # both ends of the blend
     dev = buf.to(DEV)
     q, k = dev[:, :H * dim], dev[:, H * dim:(H + G) * dim]
@@ -95,7 +95,7 @@ def attend_alone(q, k, v, gate, heads, kv_heads, dim, vdim, scale, chunk, dtype,
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("heads,kv_heads,dim,vdim,chunk,splits", [(4, 2, 48, 48, 64, 1), (4, 2, 32, 16, 24, 3), (3, 3, 16, 40, 7, 1),
+@pytest.mark.parametrize("heads,kv_heads,dim,vdim,chunk,splits", [(4, 2, 40, 40, 56, 1), (4, 2, 32, 16, 24, 3), (3, 3, 16, 40, 7, 1),
                                                                   (2, 1, 64, 64, None, 4), (6, 2, 12, 20, 10, 2)])
 def test_chunked_gated_attention_with_grouped_heads(heads, kv_heads, dim, vdim, chunk, splits, dtype):
     T = 150
@@ -109,7 +109,7 @@ def test_chunked_gated_attention_with_grouped_heads(heads, kv_heads, dim, vdim, 
     assert (got - want).abs().max() < (2e-5 if dtype == torch.float32 else 0.02)
 
 
-@pytest.mark.parametrize("chunk,page", [(64, 16), (24, 16), (7, 8), (100, 16)])
+@pytest.mark.parametrize("chunk,page", [(48, 16), (24, 16), (7, 8), (100, 16)])
 def test_a_key_just_inside_and_just_outside_a_chunk(chunk, page):
     """One key per probe is made to stand out (a large common component with the probing query): the output is that
     key's value when the key is in the query's chunk, and shows no trace of it when it is the last key of the chunk before."""
@@ -169,7 +169,7 @@ def test_relu_squared_in_the_products_epilogue(activation):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("experts,top,shared,tokens", [(8, 1, True, 1), (8, 1, True, 37), (4, 2, False, 200), (3, 3, True, 5), (16, 4, False, 70)])
+@pytest.mark.parametrize("experts,top,shared,tokens", [(6, 1, True, 1), (6, 1, True, 37), (4, 2, False, 200), (3, 3, True, 5), (16, 4, False, 70)])
 def test_experts_chosen_by_a_table(experts, top, shared, tokens, dtype):
     from damendaemon_b200.parts import GatedUnitSpec, Runtime, TableRoutedExpertsSpec
     from damendaemon_b200.parts.feed_forward import TableRoutedExperts
