@@ -88,12 +88,33 @@ gated_unit_kernel(const T* __restrict__ gate_up, int stride, T* __restrict__ out
                   float limit, float alpha) {
     dd_launch_dependents();
     dd_grid_wait();
-    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= (long long)rows * inner) return;
-    const int row = (int)(i / inner), c = (int)(i - (long long)row * inner);
-    const float g = fminf(dd_to_f32(gate_up[(size_t)row * stride + c]), limit);
-    const float u = fminf(fmaxf(dd_to_f32(gate_up[(size_t)row * stride + inner + c]), -limit), limit);
-    out[(size_t)row * out_stride + c] = dd_from_f32<T>(g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f));
+    constexpr int V = 16 / sizeof(T);          // elements of a 16-byte piece
+    const bool wide = inner % V == 0 && stride % V == 0 && out_stride % V == 0 && !(((uintptr_t)gate_up | (uintptr_t)out) & 15);
+    auto unit = [&](float g, float u) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+        return g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f);
+    };
+    if (wide) {
+        // a thread owns a piece of V neighbouring features of one row: two 16-byte loads, one 16-byte store
+        const int pieces = inner / V;
+        const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+        if (i >= (long long)rows * pieces) return;
+        const int row = (int)(i / pieces), c = (int)(i - (long long)row * pieces) * V;
+        const T* src = gate_up + (size_t)row * stride + c;
+        __align__(16) T g[V], u[V], y[V];
+        *reinterpret_cast<uint4*>(g) = *reinterpret_cast<const uint4*>(src);
+        *reinterpret_cast<uint4*>(u) = *reinterpret_cast<const uint4*>(src + inner);
+#pragma unroll
+        for (int e = 0; e < V; ++e) y[e] = dd_from_f32<T>(unit(dd_to_f32(g[e]), dd_to_f32(u[e])));
+        *reinterpret_cast<uint4*>(out + (size_t)row * out_stride + c) = *reinterpret_cast<const uint4*>(y);
+        return;
+    }
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)rows * inner; i += (long long)gridDim.x * blockDim.x) {
+        const int row = (int)(i / inner), c = (int)(i - (long long)row * inner);
+        out[(size_t)row * out_stride + c] = dd_from_f32<T>(unit(dd_to_f32(gate_up[(size_t)row * stride + c]),
+                                                                dd_to_f32(gate_up[(size_t)row * stride + inner + c])));
+    }
 }
 
 __global__ void __launch_bounds__(128)
@@ -102,13 +123,39 @@ combine_rows_kernel(const float* __restrict__ y, const int* __restrict__ pair_ro
     dd_launch_dependents();
     dd_grid_wait();
     const int t = blockIdx.x;
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float sum = 0.f;
-        for (int k = 0; k < top; ++k) {
-            const int row = pair_row[(size_t)t * top + k];
-            if (row >= 0) sum += y[(size_t)row * width + c];
+    // A block owns a token and a stretch of 128 x 4 (or 128) columns. The rows of eight choices are looked up first and
+    // then requested together, and added in the order of the choices (one row at a time, each element cost a lookup
+    // and a load one after the other: 17 us for eight tokens).
+    const bool wide = width % 4 == 0 && !(((uintptr_t)y | (uintptr_t)stream) & 15);
+    const int per = wide ? 4 : 1;
+    const int c = (blockIdx.y * 128 + threadIdx.x) * per;
+    if (c >= width) return;
+    float sum[4] = {0.f, 0.f, 0.f, 0.f};
+    for (int k0 = 0; k0 < top; k0 += 8) {
+        int row[8];
+        float4 v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) row[u] = k0 + u < top ? pair_row[(size_t)t * top + k0 + u] : -1;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (row[u] < 0) continue;
+            const float* src = y + (size_t)row[u] * width + c;
+            if (wide) v[u] = *reinterpret_cast<const float4*>(src);
+            else v[u].x = *src;
         }
-        stream[(size_t)t * width + c] += sum * weight;
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+            sum[0] += v[u].x; sum[1] += v[u].y; sum[2] += v[u].z; sum[3] += v[u].w;
+        }
+    }
+    float* dst = stream + (size_t)t * width + c;
+    if (wide) {
+        float4 s4 = *reinterpret_cast<float4*>(dst);
+        s4.x += sum[0] * weight; s4.y += sum[1] * weight; s4.z += sum[2] * weight; s4.w += sum[3] * weight;
+        *reinterpret_cast<float4*>(dst) = s4;
+    } else {
+        *dst += sum[0] * weight;
     }
 }
 }  // namespace
@@ -147,7 +194,10 @@ DD_API int dd_gated_unit(const void* gate_up, int stride, void* out, int out_str
                          float alpha, int dtype, void* stream) {
     if (rows <= 0 || inner <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
-    const int grid = dd_ceil_div((long long)rows * inner, 256);
+    // a thread takes a 16-byte piece where rows allow it, else elements in a grid-stride loop
+    const int piece = dtype == DD_F32 ? 4 : 8;
+    const bool wide = inner % piece == 0 && stride % piece == 0 && out_stride % piece == 0 && !(((uintptr_t)gate_up | (uintptr_t)out) & 15);
+    const int grid = dd_ceil_div((long long)rows * (wide ? inner / piece : inner), 256);
     if (dtype == DD_F32)
         dd_launch(gated_unit_kernel<float>, dim3(grid), dim3(256), 0, s, (const float*)gate_up, stride, (float*)out,
                   out_stride, rows, inner, limit, alpha);
@@ -162,7 +212,8 @@ DD_API int dd_gated_unit(const void* gate_up, int stride, void* out, int out_str
 DD_API int dd_combine_rows(const float* y, const int* pair_row, float* stream_rows, int n_tokens, int width, int top,
                            float weight, void* stream) {
     if (n_tokens <= 0) return 0;
-    dd_launch(combine_rows_kernel, dim3(n_tokens), dim3(128), 0, (cudaStream_t)stream, y, pair_row, stream_rows, width, top,
-              weight);
+    const bool wide = width % 4 == 0 && !(((uintptr_t)y | (uintptr_t)stream_rows) & 15);
+    dd_launch(combine_rows_kernel, dim3(n_tokens, dd_ceil_div(width, wide ? 512 : 128)), dim3(128), 0, (cudaStream_t)stream, y, pair_row,
+              stream_rows, width, top, weight);
     return dd_check_launch("dd_combine_rows");
 }

@@ -169,7 +169,7 @@ def test_relu_squared_in_the_products_epilogue(activation):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("experts,top,shared,tokens", [(6, 1, True, 1), (6, 1, True, 37), (4, 2, False, 200), (3, 3, True, 5), (16, 4, False, 70)])
+@pytest.mark.parametrize("experts,top,shared,tokens", [(6, 1, True, 1), (6, 1, True, 37), (4, 2, False, 200), (3, 3, True, 5), (16, 4, False, 70), (8, 2, False, 60)])
 def test_experts_chosen_by_a_table(experts, top, shared, tokens, dtype):
     from damendaemon_b200.parts import GatedUnitSpec, Runtime, TableRoutedExpertsSpec
     from damendaemon_b200.parts.feed_forward import TableRoutedExperts
