@@ -32,11 +32,31 @@ route_by_table_kernel(const int* __restrict__ ids, const int* __restrict__ table
     for (int r = threadIdx.x; r < n_rows; r += ROUTE_THREADS) row_token[r] = -1;
     for (int i = threadIdx.x; i < n_rows / tile; i += ROUTE_THREADS) tile_group[i] = -1;
     __syncthreads();
-    for (int pair = threadIdx.x; pair < n_pairs; pair += ROUTE_THREADS) {
-        const int id = ids[pair / top];
-        const int e = (id >= 0 && id < vocab) ? table[(size_t)id * top + pair % top] : -1;
-        if (e < 0 || e >= n_experts) atomicOr(error_flag, 1);
-        else atomicAdd(&count[e], 1);
+    // four pairs of a thread at a time: their token ids are requested together, then their table entries (one pair
+    // at a time, every pair cost two trips to memory one after the other)
+    auto experts_of = [&](int base, int* e) {
+        int id[4];
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int pair = base + u * ROUTE_THREADS;
+            id[u] = pair < n_pairs ? ids[pair / top] : -1;
+        }
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int pair = base + u * ROUTE_THREADS;
+            e[u] = (id[u] >= 0 && id[u] < vocab) ? table[(size_t)id[u] * top + pair % top] : -1;
+            if (e[u] >= n_experts) e[u] = -1;
+        }
+    };
+    for (int base = threadIdx.x; base < n_pairs; base += 4 * ROUTE_THREADS) {
+        int e[4];
+        experts_of(base, e);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            if (base + u * ROUTE_THREADS >= n_pairs) break;
+            if (e[u] < 0) atomicOr(error_flag, 1);
+            else atomicAdd(&count[e[u]], 1);
+        }
     }
     __syncthreads();
     if (threadIdx.x == 0) {
@@ -51,16 +71,21 @@ route_by_table_kernel(const int* __restrict__ ids, const int* __restrict__ table
         first[n_experts] = row;
     }
     __syncthreads();
-    for (int pair = threadIdx.x; pair < n_pairs; pair += ROUTE_THREADS) {
-        const int id = ids[pair / top];
-        const int e = (id >= 0 && id < vocab) ? table[(size_t)id * top + pair % top] : -1;
-        if (e < 0 || e >= n_experts) {
-            pair_row[pair] = -1;
-            continue;
+    for (int base = threadIdx.x; base < n_pairs; base += 4 * ROUTE_THREADS) {
+        int e[4];
+        experts_of(base, e);
+#pragma unroll
+        for (int u = 0; u < 4; ++u) {
+            const int pair = base + u * ROUTE_THREADS;
+            if (pair >= n_pairs) break;
+            if (e[u] < 0) {
+                pair_row[pair] = -1;
+                continue;
+            }
+            const int row = first[e[u]] + atomicAdd(&count[e[u]], 1);
+            pair_row[pair] = row;
+            row_token[row] = pair / top;
         }
-        const int row = first[e] + atomicAdd(&count[e], 1);
-        pair_row[pair] = row;
-        row_token[row] = pair / top;
     }
 }
 
