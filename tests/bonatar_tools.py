@@ -64,7 +64,12 @@ TINY_S = model(400, 256, [layer(_SM, moe(8, 2, 64, 3.0, shared=(64, 3.0))), laye
 _TM = mixer(3, 1, 20, 12, mask=33, rot_dims=10, base=77.0, scaling={"factor": 1.5, "original": 40, "fast": 4.0, "slow": 1.0})
 TINY_T = model(131, 100, [layer(_TM, moe(5, 2, 30, 1.0, shared=(12, 0.5))), layer(_TM, dense(52))], scale=2.5)
 
-CONFIGS = {"P": TINY_P, "Q": TINY_Q, "R": TINY_R, "S": TINY_S, "T": TINY_T}
+# U: heads of 128 with a key/value head each (the mma.sync prompt kernel and the row decode kernel in bfloat16), chunks
+# of 70, half of every head rotated, one expert of four a token
+_UM = mixer(2, 2, 128, 128, mask=70, rot_dims=64, base=300.0)
+TINY_U = model(150, 192, [layer(_UM, moe(4, 1, 48, 4.0)), layer(_UM, dense(200))], scale=4.0)
+
+CONFIGS = {"P": TINY_P, "Q": TINY_Q, "R": TINY_R, "S": TINY_S, "T": TINY_T, "U": TINY_U}
 
 
 def make_tensors(config, seed, sharpen=3.0, dtype=torch.float32):

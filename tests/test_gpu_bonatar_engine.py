@@ -10,7 +10,7 @@ from trace_tools import mixed_steps, portion_steps, tail_steps, whole_steps
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"P": [1, 5, 23, 24, 25, 49, 100, 130], "Q": [2, 6, 7, 8, 15, 50, 64, 90], "R": [1, 17, 127, 128, 129, 200, 64, 300],
-           "S": [1, 99, 100, 101, 128, 260, 300, 201], "T": [1, 32, 33, 34, 67, 150, 9, 99]}
+           "S": [1, 99, 100, 101, 128, 260, 300, 201], "T": [1, 32, 33, 34, 67, 150, 9, 99], "U": [1, 69, 70, 71, 141, 200, 64, 130]}
 FLOAT32_TOL = 2e-4
 TOL = {}
 
@@ -200,7 +200,7 @@ def test_the_replay_program_reads_this_architecture(models, tmp_path):
             assert np.abs(row - want[r][p].numpy()).max() < FLOAT32_TOL
 
 
-@pytest.mark.parametrize("name", ["R", "S"])
+@pytest.mark.parametrize("name", ["R", "S", "U"])
 def test_the_tensor_core_attention_kernels_mask_and_gate_like_the_general_one(models, name):
     """Heads of 64 in bfloat16 go to the tensor-core kernels (prompt portions; single tokens too where every head has
     its own keys): the same steps with the general kernel forced give the same rows, within what bfloat16 rounding moves
