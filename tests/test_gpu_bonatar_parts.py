@@ -139,6 +139,60 @@ def test_a_key_just_inside_and_just_outside_a_chunk(chunk, page):
     assert (got2[chunk] - value(chunk)).abs().max() < 1e-4
 
 
+def decode_alone(q, k, v, gate, heads, kv_heads, dim, vdim, scale, chunk, positions, page=8, splits=3):
+    """All T tokens' keys and values are in shuffled pages; the queries at ``positions`` are attended one by one, each as a
+    step of a single token with its keys cut into splits (what a decode step does)."""
+    from damendaemon_b200 import kernels
+    T = q.shape[0]
+    n_pages = -(-T // page) + 2
+    order = torch.randperm(n_pages, generator=torch.Generator().manual_seed(2))[: -(-T // page)].to(torch.int32)
+    table = torch.full((1, n_pages), -1, dtype=torch.int32)
+    table[0, :order.numel()] = order
+    buf = torch.cat([q, k, v, gate], dim=1).to(DEV)
+    qd, kd, vd, gd = buf.split([heads * dim, kv_heads * dim, kv_heads * vdim, heads], dim=1)
+    cache = torch.full((n_pages, kv_heads * page * (dim + vdim)), float("nan"), device=DEV) if dim != vdim else \
+        torch.full((n_pages, 2, kv_heads, page, dim), float("nan"), device=DEV)
+    entry = torch.zeros(T, dtype=torch.int32, device=DEV)
+    kernels.kv_store(kd, vd, entry, torch.arange(T, dtype=torch.int32, device=DEV), table.to(DEV), cache, kv_heads=kv_heads,
+                     head_dim=dim, v_dim=vdim)
+    out = {}
+    for p in positions:
+        pos = torch.tensor([p], dtype=torch.int32, device=DEV)
+        out[p] = kernels.attention_rows(qd[p:p + 1], cache, entry[:1], pos, table.to(DEV), heads, scale, None, n_splits=splits,
+                                        chunk=chunk, gate=gd[p:p + 1], kv_heads=kv_heads, v_dim=vdim)[0].cpu().double()
+    assert kernels.read_error_flag(DEV) == 0
+    return out
+
+
+@pytest.mark.parametrize("chunk", [None, 48, 100])
+def test_a_marked_key_far_back_in_a_prompt_and_in_decoding(chunk):
+    """Among 600 keys one, near the start, carries a mark that the last query looks for: without chunks the output is
+    that key's value, in a prompt step and in a single-token step alike; with chunks the far key is not seen, and a key
+    marked at the start of the last chunk is, while the one just before that start is not."""
+    heads, kv_heads, dim, vdim, T = 2, 2, 16, 24, 600
+    q, k = rnd(T, heads * dim, seed=40, scale=0.1), rnd(T, kv_heads * dim, seed=41, scale=0.1)
+    v, gate = rnd(T, kv_heads * vdim, seed=42), torch.full((T, heads), 30.0)
+    far, last = 3, T - 1
+    start = 0 if chunk is None else last - last % chunk          # the first key the last query sees
+    for h in range(kv_heads):
+        k[far, h * dim + 0] = 50.0                               # dimension 0: the far key
+        if chunk is not None:
+            k[start, h * dim + 1] = 40.0                         # dimension 1: the first key of the last chunk (weaker than the far one)
+            k[start - 1, h * dim + 2] = 45.0                     # dimension 2: the key just before it
+    for h in range(heads):
+        q[last, h * dim + 0] = q[last, h * dim + 1] = q[last, h * dim + 2] = 1.0
+    seen = far if chunk is None else start
+    want = torch.cat([v[seen, (h * kv_heads // heads) * vdim:(h * kv_heads // heads + 1) * vdim] for h in range(heads)]).double()
+    whole = attend_alone(q, k, v, gate, heads, kv_heads, dim, vdim, 1.0, chunk, torch.float32, page=16, splits=1)
+    assert (whole[last] - want).abs().max() < 1e-3
+    single = decode_alone(q, k, v, gate, heads, kv_heads, dim, vdim, 1.0, chunk, [last, start, max(start - 1, 0)], page=16)
+    assert (single[last] - want).abs().max() < 1e-3
+    exact = plain.grouped_attention(q.double().view(T, heads, dim), k.double().view(T, kv_heads, dim), v.double().view(T, kv_heads, vdim),
+                                    1.0, plain.visible(T, chunk)).reshape(T, -1)
+    for p, row in single.items():
+        assert (row - exact[p]).abs().max() < 1e-4, p
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_the_gated_unit(dtype):
     from damendaemon_b200 import kernels
