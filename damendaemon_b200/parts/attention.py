@@ -49,6 +49,8 @@ class Attention(Mixer):
             pad = torch.zeros((-self.qkv_w.shape[0] % 8, self.qkv_w.shape[1]), dtype=self.qkv_w.dtype, device=self.qkv_w.device)
             self.qkv_w = weights[_projection(spec)[1]] = torch.cat([self.qkv_w, pad], dim=0)
         self.qkv_b = weights[_joined(spec.qkv_bias)] if spec.qkv_bias else None
+        if self.qkv_b is not None and self.qkv_b.numel() < self.qkv_w.shape[0]:
+            self.qkv_b = torch.cat([self.qkv_b, self.qkv_b.new_zeros(self.qkv_w.shape[0] - self.qkv_b.numel())])
         self.out_w = weights[spec.out_weight]
         self.out_b = weights[spec.out_bias] if spec.out_bias else None
         self.value_dim = spec.value_dim or spec.head_dim
@@ -74,6 +76,7 @@ class Attention(Mixer):
     def tensor_decls(spec):
         q, kv = spec.n_heads * spec.head_dim, spec.n_kv_heads * spec.head_dim
         v = spec.n_kv_heads * (spec.value_dim or spec.head_dim)
+        attended = spec.n_heads * (spec.value_dim or spec.head_dim)
         gate = spec.n_heads if spec.gate_weight else 0
         total = q + kv + v + gate
         io = spec.stored_in_out
@@ -82,8 +85,7 @@ class Attention(Mixer):
         names, key = _projection(spec)
         pieces = () if isinstance(names, str) else tuple(zip(names, (matrix(q), matrix(kv), matrix(v), matrix(gate))))
         decls = [TensorDecl(key, matrix(total), "matrix", io, pieces),
-                 TensorDecl(spec.out_weight, (spec.n_heads * v // spec.n_kv_heads, spec.width) if io
-                            else (spec.width, spec.n_heads * v // spec.n_kv_heads), "matrix", io)]
+                 TensorDecl(spec.out_weight, (attended, spec.width) if io else (spec.width, attended), "matrix", io)]
         if spec.qkv_bias:
             pieces = () if isinstance(spec.qkv_bias, str) else tuple(zip(spec.qkv_bias, ((q,), (kv,), (v,))))
             decls.append(TensorDecl(_joined(spec.qkv_bias), (total,), "vector", False, pieces))

@@ -69,8 +69,9 @@ class TableRoutedExperts(FeedForward):
     The experts' gate and up matrices are stacked [E, 2 * inner, width] (gate rows, then up rows) and their down
     matrices [E, width, inner] once, when the part is built. A step sorts its (token, choice) pairs by expert on the
     device (kernels.route_by_table: every expert's rows start on a multiple of the product's row tile), gathers the
-    normed rows in that order, runs two grouped products with the gated unit between, and adds each token's rows,
-    in the order of its choices, into the float32 stream. Launch shapes depend on the step's counts only, so a step
+    normed rows in that order, runs two grouped products (on the tensor cores the first computes gate and up together
+    and applies the gated unit in its epilogue; else the unit is a kernel between them) and adds each token's rows, in
+    the order of its choices, into the float32 stream. Launch shapes depend on the step's counts only, so a step
     can be replayed from a graph."""
     graph_safe = True
 
@@ -93,7 +94,9 @@ class TableRoutedExperts(FeedForward):
         self.shared = None
         if spec.shared is not None:
             u = spec.shared
-            self.shared = (torch.cat([weights[u.gate_weight], weights[u.up_weight]], dim=0).contiguous(), weights[u.down_weight])
+            joined = torch.cat([weights.pop(u.gate_weight), weights.pop(u.up_weight)], dim=0).contiguous()
+            weights[spec.table + ":shared_gate_up"] = joined
+            self.shared = (joined, weights[u.down_weight])
 
     @staticmethod
     def tensor_decls(spec):
