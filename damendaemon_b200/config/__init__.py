@@ -1,5 +1,6 @@
 from .reader import ConfigError, parse_config_text, read_config_file
 from .bonatar import BonatarConfig
 from .gpt2 import Gpt2Config
+from .zokanex import ZokanexConfig
 
-__all__ = ["ConfigError", "parse_config_text", "read_config_file", "Gpt2Config", "BonatarConfig"]
+__all__ = ["ConfigError", "parse_config_text", "read_config_file", "Gpt2Config", "BonatarConfig", "ZokanexConfig"]

@@ -49,6 +49,19 @@ __device__ __forceinline__ float dd_activation(float u, int act) {
     return u;
 }
 
+// The gated unit's value from its gate and up products, in float32. CLAMPED: g = min(gate, limit),
+// u = clamp(up, -limit, limit), g * sigmoid(alpha g) * (u + 1); SILU: gate * sigmoid(gate) * up; GELU_TANH:
+// gelu_new(gate) * up. FAST: the exponential of the special-function unit (for results that are rounded to bfloat16).
+enum DdGated { DD_GATED_CLAMPED = 0, DD_GATED_SILU = 1, DD_GATED_GELU_TANH = 2 };
+template <bool FAST>
+__device__ __forceinline__ float dd_gated_value(float gate, float up, int form, float limit, float alpha) {
+    if (form == DD_GATED_SILU) return gate * (1.0f / (1.0f + (FAST ? __expf(-gate) : expf(-gate)))) * up;
+    if (form == DD_GATED_GELU_TANH) return dd_activation(gate, DD_ACT_GELU_NEW) * up;
+    const float g = fminf(gate, limit);
+    const float u = fminf(fmaxf(up, -limit), limit);
+    return g * (1.0f / (1.0f + (FAST ? __expf(-alpha * g) : expf(-alpha * g)))) * (u + 1.0f);
+}
+
 static inline int dd_ceil_div(long long a, long long b) { return (int)((a + b - 1) / b); }
 
 // Programmatic dependent launch. Every kernel of this library is launched so that it may start

@@ -5,7 +5,8 @@
 //
 // and, fused (DUAL), the gated unit of two such products over the same rows: the stack holds 2N rows per group, N
 // gate rows followed by N up rows, and out[r, n] = g * sigmoid(alpha g) * (u + 1) with g = min(gate, limit),
-// u = clamp(up, -limit, limit), computed in float32 from the two accumulators.
+// u = clamp(up, -limit, limit), or another form of the unit (dd_gated_value in common.cuh: silu(gate) * up, tanh-gelu(gate)
+// * up), computed in float32 from the two accumulators.
 //
 // The product is computed transposed, D^T = W . X^T: 128 weight rows are the lanes of the accumulator and a tile's
 // T rows of X (16, 32, 64 or 128) its columns, so that a step in which an expert gets a few tokens wastes no
@@ -31,6 +32,7 @@ struct GroupedParams {
     int N, K;                    // output features per group, reduction
     int rows_per_group;          // rows of W per group: N, or 2N with the gated unit
     float limit, alpha;
+    int form;                    // DD_GATED_*: which gated unit
 };
 
 template <int T, bool DUAL> struct GroupedConfig {
@@ -142,11 +144,7 @@ gemm_grouped_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
 #pragma unroll
                         for (int j = 0; j < 16; ++j) {
                             float v = __uint_as_float(g[j]);
-                            if (DUAL) {
-                                const float gate = fminf(v, p.limit);
-                                const float up = fminf(fmaxf(__uint_as_float(u[j]), -p.limit), p.limit);
-                                v = gate * (1.0f / (1.0f + __expf(-p.alpha * gate))) * (up + 1.0f);
-                            }
+                            if (DUAL) v = dd_gated_value<true>(v, __uint_as_float(u[j]), p.form, p.limit, p.alpha);
                             const size_t at = (size_t)(row0 + c0 + j) * p.ldo + n;
                             if (p.out_dtype == DD_BF16) reinterpret_cast<__nv_bfloat16*>(p.out)[at] = __float2bfloat16_rn(v);
                             else reinterpret_cast<float*>(p.out)[at] = v;
@@ -208,10 +206,10 @@ int launch_grouped(const CUtensorMap& mw, const CUtensorMap& mx, const GroupedPa
 // X [rows, K] bf16 (row stride ldx) in tiles of `tile` rows (16, 32, 64 or 128; rows a multiple of it); W: a stack of
 // `groups` matrices of rows_per_group rows of K (row stride ldw, the matrices one after the other); tile_group: device
 // array [rows / tile]. dual == 0: rows_per_group == N, out = X . W[g]^T. dual != 0: rows_per_group == 2 N (gate rows, up
-// rows), out = gated unit of the two products with `limit` and `alpha`. out: [rows, N] bf16 or f32, row stride ldo.
+// rows), out = gated unit (form: DD_GATED_*) of the two products with `limit` and `alpha`. out: [rows, N] bf16 or f32, row stride ldo.
 DD_API int dd_gemm_grouped_tcgen05(const void* X, int ldx, const void* W, int ldw, int groups, int rows_per_group,
                                    const int* tile_group, void* out, int ldo, int rows, int N, int K, int tile, int dual,
-                                   float limit, float alpha, int out_dtype, int* error_flag, void* stream) {
+                                   float limit, float alpha, int out_dtype, int* error_flag, void* stream, int form) {
     if (rows <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || ldx % 8 || ldw % 8)
         return dd_fail("dd_gemm_grouped_tcgen05: K=%d and the row strides (%d, %d) must be multiples of 8 (TMA needs 16-byte rows)", K, ldx, ldw);
@@ -222,7 +220,7 @@ DD_API int dd_gemm_grouped_tcgen05(const void* X, int ldx, const void* W, int ld
         return dd_fail("dd_gemm_grouped_tcgen05: %d rows per group do not fit N=%d", rows_per_group, N);
     GroupedParams p;
     p.tile_group = tile_group; p.out = out; p.error_flag = error_flag; p.ldo = ldo; p.out_dtype = out_dtype; p.N = N; p.K = K;
-    p.rows_per_group = rows_per_group; p.limit = limit; p.alpha = alpha;
+    p.rows_per_group = rows_per_group; p.limit = limit; p.alpha = alpha; p.form = form;
     CUtensorMap mw, mx;
     if (int e = grouped_map(&mw, W, (long long)groups * rows_per_group, K, ldw, BM, "the stacked matrices")) return e;
     if (int e = grouped_map(&mx, X, rows, K, ldx, tile, "the rows")) return e;

@@ -7,9 +7,14 @@
 //   dd_route_by_table   token ids + table [vocab, K] -> pair_row [N*K] (the row of pair (t, k)), row_token [rows]
 //                       (the token of a row, -1 for a row of padding), tile_group [rows / tile]
 //   dd_gather_rows      x [N, width] -> sorted rows (a row of padding is zeroed)
-//   dd_gated_unit       rows of [gate | up] halves -> g = min(gate, limit), u = clamp(up, -limit, limit),
-//                       y = g * sigmoid(alpha g) * (u + 1), in float32
-//   dd_combine_rows     stream[t] += sum over k of weight * y[pair_row[t*K + k]], k ascending, in float32
+//                       (ids null: token t reads row t of the table, which then holds the step's own choices)
+//   dd_route_by_score   router logits [N, >= E] -> the K experts of every token by score within the worthiest groups,
+//                       their weights, and the gate of a shared unit
+//   dd_gated_unit       rows of [gate | up] halves -> y = f(gate, up) in float32 (dd_gated_value in common.cuh: the
+//                       clamped form g * sigmoid(alpha g) * (u + 1), silu(gate) * up, or tanh-gelu(gate) * up),
+//                       optionally times a number per row
+//   dd_combine_rows     stream[t] += sum over k of weight (* pair_weight[t*K + k]) * y[pair_row[t*K + k]], k ascending,
+//                       in float32
 //
 // The order of an expert's rows among themselves depends on the order in which threads arrive; no value depends
 // on it, since every row is computed by itself and the sum over a token's experts runs in the order of its choices.
@@ -39,7 +44,7 @@ route_by_table_kernel(const int* __restrict__ ids, const int* __restrict__ table
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const int pair = base + u * ROUTE_THREADS;
-            id[u] = pair < n_pairs ? ids[pair / top] : -1;
+            id[u] = pair < n_pairs ? (ids ? ids[pair / top] : pair / top) : -1;
         }
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
@@ -89,6 +94,74 @@ route_by_table_kernel(const int* __restrict__ ids, const int* __restrict__ table
     }
 }
 
+
+// One warp per token. scores of E experts in shared memory; a run's worth by the lanes (a run each); the worthiest
+// runs and then the best experts by repeated arg-max over the warp, the lowest index winning a tie.
+__global__ void __launch_bounds__(128)
+route_by_score_kernel(const float* __restrict__ logits, int ld, int n_tokens, int n_experts, int top, int groups, int keep,
+                      float weight_scale, int gate_col, int* __restrict__ chosen, float* __restrict__ pair_weight,
+                      float* __restrict__ shared_scale) {
+    extern __shared__ float route_smem[];        // per warp: [E] scores, [groups] worths
+    dd_launch_dependents();
+    dd_grid_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x * 4 + warp;
+    if (t >= n_tokens) return;
+    float* score = route_smem + warp * (n_experts + groups);
+    float* worth = score + n_experts;
+    const float* z = logits + (size_t)t * ld;
+    for (int e = lane; e < n_experts; e += 32) score[e] = 1.0f / (1.0f + expf(-z[e]));
+    if (lane == 0 && shared_scale) shared_scale[t] = gate_col >= 0 ? 1.0f / (1.0f + expf(-z[gate_col])) : 1.0f;
+    __syncwarp();
+    const int per = n_experts / groups;
+    if (groups > 1) {
+        for (int g = lane; g < groups; g += 32) {
+            float best = -1.f, second = -1.f;            // scores lie in (0, 1)
+            for (int i = 0; i < per; ++i) {
+                const float s = score[g * per + i];
+                if (s > best) { second = best; best = s; }
+                else if (s > second) second = s;
+            }
+            worth[g] = best + (per > 1 ? second : 0.f);
+        }
+        __syncwarp();
+        // keep the worthiest runs: the others' scores are struck out
+        for (int round = 0; round < keep; ++round) {
+            float best = -1.f;
+            int at = 0x7fffffff;
+            for (int g = lane; g < groups; g += 32)
+                if (worth[g] > best) { best = worth[g]; at = g; }
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+                if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+            }
+            if (lane == 0 && at < groups) worth[at] = -2.f;     // marked as kept
+            __syncwarp();
+        }
+        for (int e = lane; e < n_experts; e += 32)
+            if (worth[e / per] != -2.f) score[e] = -1.f;
+        __syncwarp();
+    }
+    for (int k = 0; k < top; ++k) {
+        float best = -1.f;
+        int at = 0x7fffffff;
+        for (int e = lane; e < n_experts; e += 32)
+            if (score[e] > best) { best = score[e]; at = e; }
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (ob > best || (ob == best && oa < at)) { best = ob; at = oa; }
+        }
+        if (lane == 0) {
+            chosen[(size_t)t * top + k] = at < n_experts ? at : -1;
+            pair_weight[(size_t)t * top + k] = at < n_experts ? best * weight_scale : 0.f;
+            if (at < n_experts) score[at] = -1.f;
+        }
+        __syncwarp();
+    }
+}
+
 template <typename T>
 __global__ void __launch_bounds__(128)
 gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ row_token, T* __restrict__ out, int width) {
@@ -110,16 +183,12 @@ gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ row_token, T
 template <typename T>
 __global__ void __launch_bounds__(256)
 gated_unit_kernel(const T* __restrict__ gate_up, int stride, T* __restrict__ out, int out_stride, int rows, int inner,
-                  float limit, float alpha) {
+                  float limit, float alpha, int form, const float* __restrict__ row_scale) {
     dd_launch_dependents();
     dd_grid_wait();
     constexpr int V = 16 / sizeof(T);          // elements of a 16-byte piece
     const bool wide = inner % V == 0 && stride % V == 0 && out_stride % V == 0 && !(((uintptr_t)gate_up | (uintptr_t)out) & 15);
-    auto unit = [&](float g, float u) {
-        g = fminf(g, limit);
-        u = fminf(fmaxf(u, -limit), limit);
-        return g * (1.0f / (1.0f + expf(-alpha * g))) * (u + 1.0f);
-    };
+    auto unit = [&](float g, float u) { return dd_gated_value<false>(g, u, form, limit, alpha); };
     if (wide) {
         // a thread owns a piece of V neighbouring features of one row: two 16-byte loads, one 16-byte store
         const int pieces = inner / V;
@@ -130,21 +199,23 @@ gated_unit_kernel(const T* __restrict__ gate_up, int stride, T* __restrict__ out
         __align__(16) T g[V], u[V], y[V];
         *reinterpret_cast<uint4*>(g) = *reinterpret_cast<const uint4*>(src);
         *reinterpret_cast<uint4*>(u) = *reinterpret_cast<const uint4*>(src + inner);
+        const float by = row_scale ? row_scale[row] : 1.0f;
 #pragma unroll
-        for (int e = 0; e < V; ++e) y[e] = dd_from_f32<T>(unit(dd_to_f32(g[e]), dd_to_f32(u[e])));
+        for (int e = 0; e < V; ++e) y[e] = dd_from_f32<T>(unit(dd_to_f32(g[e]), dd_to_f32(u[e])) * by);
         *reinterpret_cast<uint4*>(out + (size_t)row * out_stride + c) = *reinterpret_cast<const uint4*>(y);
         return;
     }
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < (long long)rows * inner; i += (long long)gridDim.x * blockDim.x) {
         const int row = (int)(i / inner), c = (int)(i - (long long)row * inner);
         out[(size_t)row * out_stride + c] = dd_from_f32<T>(unit(dd_to_f32(gate_up[(size_t)row * stride + c]),
-                                                                dd_to_f32(gate_up[(size_t)row * stride + inner + c])));
+                                                                dd_to_f32(gate_up[(size_t)row * stride + inner + c])) *
+                                                           (row_scale ? row_scale[row] : 1.0f));
     }
 }
 
 __global__ void __launch_bounds__(128)
 combine_rows_kernel(const float* __restrict__ y, const int* __restrict__ pair_row, float* __restrict__ stream, int width,
-                    int top, float weight) {
+                    int top, float weight, const float* __restrict__ pair_weight) {
     dd_launch_dependents();
     dd_grid_wait();
     const int t = blockIdx.x;
@@ -159,8 +230,12 @@ combine_rows_kernel(const float* __restrict__ y, const int* __restrict__ pair_ro
     for (int k0 = 0; k0 < top; k0 += 8) {
         int row[8];
         float4 v[8];
+        float by[8];
 #pragma unroll
-        for (int u = 0; u < 8; ++u) row[u] = k0 + u < top ? pair_row[(size_t)t * top + k0 + u] : -1;
+        for (int u = 0; u < 8; ++u) {
+            row[u] = k0 + u < top ? pair_row[(size_t)t * top + k0 + u] : -1;
+            by[u] = (pair_weight && k0 + u < top) ? pair_weight[(size_t)t * top + k0 + u] : 1.0f;
+        }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
             v[u] = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -171,7 +246,8 @@ combine_rows_kernel(const float* __restrict__ y, const int* __restrict__ pair_ro
         }
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-            sum[0] += v[u].x; sum[1] += v[u].y; sum[2] += v[u].z; sum[3] += v[u].w;
+            sum[0] = fmaf(v[u].x, by[u], sum[0]); sum[1] = fmaf(v[u].y, by[u], sum[1]);
+            sum[2] = fmaf(v[u].z, by[u], sum[2]); sum[3] = fmaf(v[u].w, by[u], sum[3]);
         }
     }
     float* dst = stream + (size_t)t * width + c;
@@ -201,6 +277,25 @@ DD_API int dd_route_by_table(const int* ids, const int* table, int n_tokens, int
     return dd_check_launch("dd_route_by_table");
 }
 
+// logits: float32 [n_tokens] rows of ld values, the first n_experts the router's; score = sigmoid(logit). The experts
+// form `groups` equal runs of neighbours, a run's worth is the sum of its two largest scores (of its one), only the `keep`
+// worthiest runs stay eligible; the `top` largest eligible scores win. chosen: int32 [n_tokens, top] by falling score
+// (-1 where fewer were eligible), pair_weight: float32 [n_tokens, top] = score * weight_scale. shared_scale (or null):
+// float32 [n_tokens] = sigmoid(logits[t][gate_col]), 1 with gate_col < 0.
+DD_API int dd_route_by_score(const float* logits, int ld, int n_tokens, int n_experts, int top, int groups, int keep,
+                             float weight_scale, int gate_col, int* chosen, float* pair_weight, float* shared_scale,
+                             void* stream) {
+    if (n_tokens <= 0) return 0;
+    if (n_experts <= 0 || top <= 0 || top > n_experts || groups <= 0 || n_experts % groups || keep <= 0 || keep > groups ||
+        gate_col >= ld || n_experts > ld)
+        return dd_fail("dd_route_by_score: %d of %d experts in %d groups of which %d stay, rows of %d", top, n_experts, groups, keep, ld);
+    const size_t smem = 4 * (size_t)(n_experts + groups) * sizeof(float);
+    if (smem > 48 * 1024) return dd_fail("dd_route_by_score: %d experts are more than a warp's shared memory holds", n_experts);
+    dd_launch(route_by_score_kernel, dim3(dd_ceil_div(n_tokens, 4)), dim3(128), smem, (cudaStream_t)stream, logits, ld, n_tokens,
+              n_experts, top, groups, keep, weight_scale, gate_col, chosen, pair_weight, shared_scale);
+    return dd_check_launch("dd_route_by_score");
+}
+
 DD_API int dd_gather_rows(const void* x, const int* row_token, void* out, int n_rows, int width, int dtype, void* stream) {
     if (n_rows <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
@@ -215,8 +310,9 @@ DD_API int dd_gather_rows(const void* x, const int* row_token, void* out, int n_
 }
 
 // gate_up: rows of `stride` elements, the gate's `inner` values followed by the up projection's.
+// form: DD_GATED_* (common.cuh); row_scale: float32 [rows] or null.
 DD_API int dd_gated_unit(const void* gate_up, int stride, void* out, int out_stride, int rows, int inner, float limit,
-                         float alpha, int dtype, void* stream) {
+                         float alpha, int dtype, void* stream, int form, const float* row_scale) {
     if (rows <= 0 || inner <= 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     // a thread takes a 16-byte piece where rows allow it, else elements in a grid-stride loop
@@ -225,20 +321,20 @@ DD_API int dd_gated_unit(const void* gate_up, int stride, void* out, int out_str
     const int grid = dd_ceil_div((long long)rows * (wide ? inner / piece : inner), 256);
     if (dtype == DD_F32)
         dd_launch(gated_unit_kernel<float>, dim3(grid), dim3(256), 0, s, (const float*)gate_up, stride, (float*)out,
-                  out_stride, rows, inner, limit, alpha);
+                  out_stride, rows, inner, limit, alpha, form, row_scale);
     else if (dtype == DD_BF16)
         dd_launch(gated_unit_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, s, (const __nv_bfloat16*)gate_up, stride,
-                  (__nv_bfloat16*)out, out_stride, rows, inner, limit, alpha);
+                  (__nv_bfloat16*)out, out_stride, rows, inner, limit, alpha, form, row_scale);
     else
         return dd_fail("dd_gated_unit: unknown dtype %d", dtype);
     return dd_check_launch("dd_gated_unit");
 }
 
 DD_API int dd_combine_rows(const float* y, const int* pair_row, float* stream_rows, int n_tokens, int width, int top,
-                           float weight, void* stream) {
+                           float weight, void* stream, const float* pair_weight) {
     if (n_tokens <= 0) return 0;
     const bool wide = width % 4 == 0 && !(((uintptr_t)y | (uintptr_t)stream_rows) & 15);
     dd_launch(combine_rows_kernel, dim3(n_tokens, dd_ceil_div(width, wide ? 512 : 128)), dim3(128), 0, (cudaStream_t)stream, y, pair_row,
-              stream_rows, width, top, weight);
+              stream_rows, width, top, weight, pair_weight);
     return dd_check_launch("dd_combine_rows");
 }

@@ -15,6 +15,7 @@ from .csrc import build
 
 F32, BF16 = 0, 1
 ACTIVATIONS = {None: 0, "none": 0, "gelu_new": 1, "gelu": 2, "relu2": 3}
+GATED_FORMS = {"clamped_swish": 0, "silu": 1, "gelu_tanh": 2}     # the forms of a gated unit (csrc/common.cuh)
 
 _c_int, _c_float, _c_void = ctypes.c_int, ctypes.c_float, ctypes.c_void_p
 
@@ -35,8 +36,13 @@ _SIGNATURES = {
         "dd_gemm_simt_grouped": [_c_void, _c_int, _c_void, _c_int, ctypes.c_longlong, _c_void, _c_void, _c_int] + [_c_int] * 6 + [_c_void],
         "dd_route_by_table": [_c_void, _c_void] + [_c_int] * 6 + [_c_void] * 5,
         "dd_gather_rows": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void],
-        "dd_gated_unit": [_c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_void],
-        "dd_combine_rows": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_float, _c_void],
+        "dd_gated_unit": [_c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_void, _c_int, _c_void],
+        "dd_combine_rows": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_float, _c_void, _c_void],
+        "dd_route_by_score": [_c_void] + [_c_int] * 6 + [_c_float, _c_int, _c_void, _c_void, _c_void, _c_void],
+        "dd_head_norm_rotary": [_c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_float] + [_c_int] * 7 + [_c_void],
+        "dd_retention": [_c_void, _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_void,
+                         _c_float, _c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void],
+        "dd_retention_finish": [_c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
         "dd_gemm_simt": [_c_void, _c_int, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int] + [_c_int] * 6 + [_c_void],
         "dd_kv_store": [_c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_void] + [_c_int] * 7 + [_c_void, _c_void],
         "dd_attention_rows": [_c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int, _c_void, _c_void]
@@ -49,7 +55,7 @@ _SIGNATURES = {
     "tensor": {
         "dd_gemm_tcgen05_plan": [_c_int, _c_int, _c_int, _c_int, _c_void, _c_void],
         "dd_gemm_grouped_tcgen05": [_c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int] + [_c_int] * 5
-                                   + [_c_float, _c_float, _c_int, _c_void, _c_void],
+                                   + [_c_float, _c_float, _c_int, _c_void, _c_void, _c_int],
         "dd_wait_probe": [ctypes.c_ulonglong, _c_void, _c_void, _c_void],
         "dd_attention_decode_supported": [_c_int] * 4,
         "dd_attention_prefill_supported": [_c_int] * 4,
@@ -289,6 +295,62 @@ def rotary(q, k, positions, freqs, magnitude, q_heads, k_heads, head_dim, interl
     return q, k
 
 
+def head_norm_rotary(q, k, positions, q_weight, k_weight, eps, q_heads, k_heads, head_dim, freqs=None, interleaved=True):
+    """In place and in one pass: every head of q (and of k, a row view of the same buffer, or None with k_heads 0)
+    becomes x / sqrt(mean(x^2) + eps) * weight (q_weight for query heads, k_weight for key heads, float32 [head_dim];
+    None: that kind is not normed), then the first 2 * len(freqs) dimensions of the head are rotated by position * freqs
+    as in ``rotary`` (freqs None: no rotation). All float32 inside."""
+    if k is not None and (q.stride(0) != k.stride(0) or k.stride(1) != 1 or q.dtype != k.dtype or k.shape[1] != k_heads * head_dim):
+        raise KernelError("head_norm_rotary: q and k must be row views of one buffer")
+    if q.stride(1) != 1 or q.shape[1] != q_heads * head_dim or (k is None) != (k_heads == 0):
+        raise KernelError("head_norm_rotary: shapes do not fit the heads")
+    for w in (q_weight, k_weight):
+        if w is not None and (w.numel() != head_dim or w.dtype != torch.float32 or not w.is_contiguous()):
+            raise KernelError("head_norm_rotary: a weight must be float32 [head_dim]")
+    n_pairs = 0 if freqs is None else freqs.numel()
+    _call(library("core"), "dd_head_norm_rotary", _ptr(q, "q"), _ptr(k, "k"), q.stride(0), _ptr(positions, "positions", torch.int32),
+          _ptr(freqs, "freqs", torch.float32), _ptr(q_weight, "q_weight"), _ptr(k_weight, "k_weight"), float(eps), q.shape[0],
+          q_heads, k_heads, head_dim, n_pairs, 1 if interleaved else 0, _dt(q.dtype), _stream())
+    return q, k
+
+
+def retention(q, k, v, positions, entry_start, entry_slot, decay, key_scale, state, freqs=None, interleaved=True, out=None):
+    """The retention recurrence of a step: per entry (rows entry_start[e] .. entry_start[e+1]) and head, from the
+    state in row entry_slot[e] of ``state`` (float32 [slots, heads, dv, dk], read and written), token by token:
+    S = decay * S + k' v^T, o = S^T q', with q', k' rotated by position * freqs (None: not rotated) and k' times
+    key_scale. q, k [N, heads*dk], v [N, heads*dv]: row views of one buffer. Returns o float32 [N, heads*dv]."""
+    n_slots, heads, dv, dk = state.shape
+    if not (q.stride(0) == k.stride(0) == v.stride(0)) or q.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1 or \
+            not (q.dtype == k.dtype == v.dtype):
+        raise KernelError("retention: q, k and v must be row views of one buffer")
+    if q.shape[1] != heads * dk or k.shape[1] != heads * dk or v.shape[1] != heads * dv or state.dtype != torch.float32 or \
+            not state.is_contiguous() or decay.numel() != heads:
+        raise KernelError("retention: shapes do not fit the state")
+    n = q.shape[0]
+    if out is None:
+        out = torch.empty((n, heads * dv), dtype=torch.float32, device=q.device)
+    _call(library("core"), "dd_retention", _ptr(q, "q"), _ptr(k, "k"), _ptr(v, "v"), q.stride(0),
+          _ptr(positions, "positions", torch.int32), _ptr(entry_start, "entry_start", torch.int32),
+          _ptr(entry_slot, "entry_slot", torch.int32), entry_slot.numel(), _ptr(freqs, "freqs", torch.float32),
+          0 if freqs is None else freqs.numel(), 1 if interleaved else 0, _ptr(decay, "decay", torch.float32), float(key_scale),
+          _ptr(state, "state"), n_slots, _ptr(out, "out", torch.float32), heads, dk, dv, _dt(q.dtype),
+          _ptr(error_flag(q.device)), _stream())
+    return out
+
+
+def retention_finish(o, gate, heads, eps, out_dtype, out=None):
+    """out[t, head] = o[t, head] / sqrt(mean(o[t, head]^2) + eps) * silu(gate[t, head]); o float32 [N, heads*dv], gate a
+    row view [N, heads*dv] in out_dtype."""
+    n, total = o.shape
+    if gate.shape != (n, total) or gate.stride(1) != 1 or gate.dtype != out_dtype or not o.is_contiguous() or total % heads:
+        raise KernelError("retention_finish: the gate does not fit the read-out")
+    if out is None:
+        out = torch.empty((n, total), dtype=out_dtype, device=o.device)
+    _call(library("core"), "dd_retention_finish", _ptr(o, "o", torch.float32), _ptr(gate, "gate"), gate.stride(0), _ptr(out, "out"),
+          out.stride(0), n, heads, total // heads, float(eps), _dt(out_dtype), _stream())
+    return out
+
+
 def gemm_simt(a, w, bias=None, residual=None, activation=None, out_dtype=None, out=None):
     """act(a @ w.T + bias) (+ residual) with CUDA-core float32 multiply-add. a [M,K], w [N,K]."""
     _rows(a, "a"), _rows(w, "w")
@@ -372,15 +434,33 @@ def grouped_rows(n_tokens, top, n_experts, tile):
 
 
 def route_by_table(ids, table, n_experts, tile):
-    """ids int32 [N], table int32 [vocab, K] -> (pair_row [N*K], row_token [rows], tile_group [rows/tile])."""
-    n, (vocab, top) = ids.numel(), table.shape
+    """ids int32 [N], table int32 [vocab, K] -> (pair_row [N*K], row_token [rows], tile_group [rows/tile]). ids None:
+    token t reads row t of the table (the step's own choices, [N, K], as ``route_by_score`` leaves them)."""
+    vocab, top = table.shape
+    n = vocab if ids is None else ids.numel()
     rows = grouped_rows(n, top, n_experts, tile)
-    pair_row = torch.empty((n * top,), dtype=torch.int32, device=ids.device)
-    row_token = torch.empty((rows,), dtype=torch.int32, device=ids.device)
-    tile_group = torch.empty((rows // tile,), dtype=torch.int32, device=ids.device)
+    pair_row = torch.empty((n * top,), dtype=torch.int32, device=table.device)
+    row_token = torch.empty((rows,), dtype=torch.int32, device=table.device)
+    tile_group = torch.empty((rows // tile,), dtype=torch.int32, device=table.device)
     _call(library("core"), "dd_route_by_table", _ptr(ids, "ids", torch.int32), _ptr(table, "table", torch.int32), n, vocab, top,
-          n_experts, tile, rows, _ptr(pair_row), _ptr(row_token), _ptr(tile_group), _ptr(error_flag(ids.device)), _stream())
+          n_experts, tile, rows, _ptr(pair_row), _ptr(row_token), _ptr(tile_group), _ptr(error_flag(table.device)), _stream())
     return pair_row, row_token, tile_group
+
+
+def route_by_score(logits, n_experts, top, groups=1, keep=1, weight_scale=1.0, gate_col=None):
+    """Router logits float32 [N, >= n_experts] -> (chosen int32 [N, top], pair_weight float32 [N, top], shared_scale
+    float32 [N] or None). score = sigmoid(logit); the experts form ``groups`` equal runs of neighbours, a run's worth is
+    the sum of its two largest scores, only the ``keep`` worthiest runs stay eligible; the ``top`` largest eligible
+    scores win, each weighing score * weight_scale. gate_col: the column of ``logits`` whose sigmoid is a shared
+    unit's gate."""
+    _rows(logits, "logits")
+    n = logits.shape[0]
+    chosen = torch.empty((n, top), dtype=torch.int32, device=logits.device)
+    weight = torch.empty((n, top), dtype=torch.float32, device=logits.device)
+    shared = None if gate_col is None else torch.empty((n,), dtype=torch.float32, device=logits.device)
+    _call(library("core"), "dd_route_by_score", _ptr(logits, "logits", torch.float32), logits.stride(0), n, n_experts, top, groups,
+          keep, float(weight_scale), -1 if gate_col is None else int(gate_col), _ptr(chosen), _ptr(weight), _ptr(shared), _stream())
+    return chosen, weight, shared
 
 
 def gather_rows(x, row_token):
@@ -419,9 +499,10 @@ GROUPED_TCGEN05_TILES = (16, 32, 64, 128)
 
 def gemm_grouped_tcgen05(a, w, tile_group, tile, gated=None, out_dtype=None):
     """a [rows, K] bfloat16 in tiles of ``tile`` rows (one of GROUPED_TCGEN05_TILES); w [groups, N, K] bfloat16; tile i
-    is multiplied with w[tile_group[i]] on the tensor cores (skipped where that is negative). gated=(limit, alpha): w
-    holds gate rows then up rows ([groups, 2 * inner, K]) and the result is the gated unit of the two products,
-    [rows, inner], computed in float32 in the product's epilogue."""
+    is multiplied with w[tile_group[i]] on the tensor cores (skipped where that is negative). gated=(limit, alpha) or
+    (limit, alpha, form): w holds gate rows then up rows ([groups, 2 * inner, K]) and the result is the gated unit (form:
+    one of GATED_FORMS, the clamped one by default) of the two products, [rows, inner], computed in float32 in the
+    product's epilogue."""
     _rows(a, "a")
     if w.dim() != 3 or not w.is_contiguous() or w.shape[2] != a.shape[1] or w.dtype != torch.bfloat16 or a.dtype != torch.bfloat16:
         raise KernelError(f"grouped gemm: a {tuple(a.shape)} {a.dtype} does not fit w {tuple(w.shape)} {w.dtype}")
@@ -430,30 +511,38 @@ def gemm_grouped_tcgen05(a, w, tile_group, tile, gated=None, out_dtype=None):
     N = per_group // 2 if gated else per_group
     out_dtype = out_dtype or torch.bfloat16
     out = torch.empty((rows, N), dtype=out_dtype, device=a.device)
-    limit, alpha = gated if gated else (0.0, 0.0)
+    limit, alpha, form = (tuple(gated) + ("clamped_swish",))[:3] if gated else (0.0, 0.0, "clamped_swish")
     _call(library("tensor"), "dd_gemm_grouped_tcgen05", _ptr(a, "a"), a.stride(0), _ptr(w, "w"), w.stride(1), groups, per_group,
           _ptr(tile_group, "tile_group", torch.int32), _ptr(out), out.stride(0), rows, N, K, int(tile), 1 if gated else 0,
-          float(limit), float(alpha), _dt(out_dtype), _ptr(error_flag(a.device)), _stream())
+          float(limit), float(alpha), _dt(out_dtype), _ptr(error_flag(a.device)), _stream(), GATED_FORMS[form])
     return out
 
 
-def gated_unit(gate_up, limit, alpha, out=None):
-    """rows of [gate | up] halves -> min(gate, limit) * sigmoid(alpha * min(gate, limit)) * (clamp(up, -limit, limit) + 1)."""
+def gated_unit(gate_up, limit, alpha, out=None, form="clamped_swish", row_scale=None):
+    """rows of [gate | up] halves -> the gated unit's value. form 'clamped_swish': min(gate, limit) * sigmoid(alpha *
+    min(gate, limit)) * (clamp(up, -limit, limit) + 1); 'silu': gate * sigmoid(gate) * up; 'gelu_tanh': gelu_new(gate) * up.
+    row_scale: float32 [rows], multiplies a row's values (in float32, before they are rounded)."""
     _rows(gate_up, "gate_up")
     rows, inner = gate_up.shape[0], gate_up.shape[1] // 2
     if out is None:
         out = torch.empty((rows, inner), dtype=gate_up.dtype, device=gate_up.device)
+    if row_scale is not None and (row_scale.numel() != rows or row_scale.dtype != torch.float32 or not row_scale.is_contiguous()):
+        raise KernelError("gated_unit: row_scale must be float32 [rows]")
     _call(library("core"), "dd_gated_unit", _ptr(gate_up, "gate_up"), gate_up.stride(0), _ptr(out), out.stride(0), rows, inner,
-          float(limit), float(alpha), _dt(gate_up.dtype), _stream())
+          float(limit), float(alpha), _dt(gate_up.dtype), _stream(), GATED_FORMS[form], _ptr(row_scale, "row_scale"))
     return out
 
 
-def combine_rows(y, pair_row, stream_rows, top, weight):
-    """stream_rows[t] += weight * sum over k of y[pair_row[t*top + k]] (float32, k ascending), in place."""
+def combine_rows(y, pair_row, stream_rows, top, weight, pair_weight=None):
+    """stream_rows[t] += weight * sum over k of (pair_weight[t*top + k] *) y[pair_row[t*top + k]] (float32, k ascending),
+    in place. pair_weight: float32 [N * top] or None."""
     if y.dtype != torch.float32 or stream_rows.dtype != torch.float32 or not y.is_contiguous() or not stream_rows.is_contiguous():
         raise KernelError("combine_rows: float32 contiguous rows wanted")
+    if pair_weight is not None and (pair_weight.numel() != stream_rows.shape[0] * top or pair_weight.dtype != torch.float32
+                                    or not pair_weight.is_contiguous()):
+        raise KernelError("combine_rows: pair_weight must be float32 [tokens * top]")
     _call(library("core"), "dd_combine_rows", _ptr(y), _ptr(pair_row, "pair_row", torch.int32), _ptr(stream_rows),
-          stream_rows.shape[0], stream_rows.shape[1], int(top), float(weight), _stream())
+          stream_rows.shape[0], stream_rows.shape[1], int(top), float(weight), _stream(), _ptr(pair_weight, "pair_weight"))
     return stream_rows
 
 

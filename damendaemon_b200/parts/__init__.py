@@ -3,6 +3,6 @@ from .model import DecoderModel, cache_needs, tensor_decls
 from .registry import (ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, register_arrangement,
                        register_embedding, register_feed_forward, register_head, register_mixer, register_norm,
                        register_position)
-from .spec import (AttentionSpec, DenseFeedForwardSpec, EmbeddingSpec, GatedUnitSpec, HeadSpec, LayerSpec, LongContextBlend,
-                   ModelSpec, NoFeedForwardSpec, NormSpec, PositionSpec, RotarySpec, RunEntry, TableRoutedExpertsSpec,
-                   TensorDecl)
+from .spec import (AttentionSpec, DenseFeedForwardSpec, EmbeddingSpec, GatedFeedForwardSpec, GatedUnitSpec, HeadSpec, LayerSpec,
+                   LongContextBlend, ModelSpec, NoFeedForwardSpec, NormSpec, PositionSpec, RetentionSpec, RotarySpec, RunEntry,
+                   ScoreRoutedExpertsSpec, TableRoutedExpertsSpec, TensorDecl)

@@ -6,13 +6,17 @@ are: a value head of another size than a key head; a chunked mask (positions in 
 counted from the start of the sequence, nothing seen across a border); a gate per head,
 sigmoid of one more projection of the mixer's input, on the head's output before the
 output projection (its rows are joined to the fused projection); a rotary position
-encoding of the mixer's own. The kernels read keys and values from the cache pages only, so
+encoding of the mixer's own; an RMS norm over every query head and every key head before
+that rotation (one kernel does both); no keys and values of its own (the mixer then
+projects queries only and reads the cache of another stop of the run order through its own
+mask). The kernels read keys and values from the cache pages only, so
 a portion of a prompt sees earlier portions exactly as a decoded token sees its context.
 """
 from __future__ import annotations
 
 import torch
 
+from .. import kernels
 from ..cache.manager import PagedKeyValues
 from .paged_attention import prompt_key_block
 from .interfaces import Mixer
@@ -29,6 +33,10 @@ def _joined(names):
 def _projection(spec):
     """(names of the pieces of the fused projection, or its one name; the key the joined tensor is found under)."""
     names = spec.qkv_weight
+    if not spec.own_keys_values:
+        if isinstance(names, str) or len(names) != 1:
+            raise ValueError("a mixer without keys and values of its own names its query projection alone")
+        names = tuple(names)
     if spec.gate_weight:
         if isinstance(names, str):
             raise ValueError("a gate's rows are joined to separate query, key and value projections")
@@ -55,8 +63,12 @@ class Attention(Mixer):
         self.out_b = weights[spec.out_bias] if spec.out_bias else None
         self.value_dim = spec.value_dim or spec.head_dim
         self.q_width = spec.n_heads * spec.head_dim
-        self.kv_width = spec.n_kv_heads * spec.head_dim
-        self.v_width = spec.n_kv_heads * self.value_dim
+        self.kv_width = spec.n_kv_heads * spec.head_dim if spec.own_keys_values else 0
+        self.v_width = spec.n_kv_heads * self.value_dim if spec.own_keys_values else 0
+        self.query_norm = weights[spec.query_norm] if spec.query_norm else None
+        self.key_norm = weights[spec.key_norm] if spec.key_norm else None
+        if self.key_norm is not None and not spec.own_keys_values:
+            raise ValueError("a mixer without keys of its own has no key norm")
         plain = self.value_dim == spec.head_dim
         if spec.head_dim > 256 or self.value_dim > 256:
             raise ValueError(f"head sizes {spec.head_dim} and {self.value_dim} are not supported (at most 256)")
@@ -76,6 +88,8 @@ class Attention(Mixer):
     def tensor_decls(spec):
         q, kv = spec.n_heads * spec.head_dim, spec.n_kv_heads * spec.head_dim
         v = spec.n_kv_heads * (spec.value_dim or spec.head_dim)
+        if not spec.own_keys_values:
+            kv = v = 0
         attended = spec.n_heads * (spec.value_dim or spec.head_dim)
         gate = spec.n_heads if spec.gate_weight else 0
         total = q + kv + v + gate
@@ -83,7 +97,8 @@ class Attention(Mixer):
         matrix = lambda n: (spec.width, n) if io else (n, spec.width)
         # one fused projection in the checkpoint, or separate query, key and value (and gate) projections joined at load
         names, key = _projection(spec)
-        pieces = () if isinstance(names, str) else tuple(zip(names, (matrix(q), matrix(kv), matrix(v), matrix(gate))))
+        shapes = (matrix(q), matrix(kv), matrix(v), matrix(gate)) if spec.own_keys_values else (matrix(q), matrix(gate))
+        pieces = () if isinstance(names, str) else tuple(zip(names, shapes))
         decls = [TensorDecl(key, matrix(total), "matrix", io, pieces),
                  TensorDecl(spec.out_weight, (attended, spec.width) if io else (spec.width, attended), "matrix", io)]
         if spec.qkv_bias:
@@ -91,22 +106,45 @@ class Attention(Mixer):
             decls.append(TensorDecl(_joined(spec.qkv_bias), (total,), "vector", False, pieces))
         if spec.out_bias:
             decls.append(TensorDecl(spec.out_bias, (spec.width,), "vector"))
+        for name in (spec.query_norm, spec.key_norm):
+            if name:
+                decls.append(TensorDecl(name, (spec.head_dim,), "vector"))
         return decls
 
     @staticmethod
     def cache_needs(spec):
+        if not spec.own_keys_values:
+            return []
         value_dim = None if spec.value_dim in (None, spec.head_dim) else spec.value_dim
-        return [PagedKeyValues(spec.n_kv_heads, spec.head_dim, spec.window, value_dim, spec.chunk)]
+        # the cache keeps what the widest mask that reads it needs (other stops may read it through masks of their own)
+        kept = spec.window if spec.keep_window is None else (None if spec.keep_window == "all" else int(spec.keep_window))
+        return [PagedKeyValues(spec.n_kv_heads, spec.head_dim, kept, value_dim, spec.chunk)]
 
     def forward(self, y, residual, ctx, cache, position):
         s = self.spec
         qkv = linear(self.runtime, y, self.qkv_w, self.qkv_b)
         q = qkv[:, :self.q_width]
-        k = qkv[:, self.q_width:self.q_width + self.kv_width]
-        v = qkv[:, self.q_width + self.kv_width:self.q_width + self.kv_width + self.v_width]
+        k = v = None
+        if s.own_keys_values:
+            k = qkv[:, self.q_width:self.q_width + self.kv_width]
+            v = qkv[:, self.q_width + self.kv_width:self.q_width + self.kv_width + self.v_width]
+        elif cache.writable:
+            raise ValueError("a mixer without keys and values of its own must read another stop's cache (RunEntry.cache_of)")
         gate = qkv[:, self.q_width + self.kv_width + self.v_width:][:, :s.n_heads] if s.gate_weight else None
         q, k = position.on_query_key(q, k, ctx)
-        if self.rotary is not None:
+        if self.query_norm is not None or self.key_norm is not None or (k is None and self.rotary is not None):
+            # the heads' norm and the rotation in one pass over the projection's output (the normed value is rotated as
+            # float32); a rotation that also scales cosine and sine follows as a pass of its own
+            fused = self.rotary is not None and self.rotary.magnitude == 1.0
+            kernels.head_norm_rotary(q, k, ctx.positions, self.query_norm, self.key_norm, s.head_norm_eps, s.n_heads,
+                                     s.n_kv_heads if k is not None else 0, s.head_dim,
+                                     freqs=self.rotary.freqs if fused else None,
+                                     interleaved=self.rotary.spec.interleaved if fused else True)
+            if self.rotary is not None and not fused:
+                if k is None:
+                    raise ValueError("a rotation with scaled cosines needs keys of the mixer's own")
+                q, k = self.rotary.on_query_key(q, k, ctx)
+        elif self.rotary is not None:
             q, k = self.rotary.on_query_key(q, k, ctx)
         attended = ctx.attend(q, k, v, cache, s.n_heads, s.scale, s.window, gate=gate, **self.mask)
         return linear(self.runtime, attended, self.out_w, self.out_b, residual=residual, out_dtype=residual.dtype,

@@ -2,6 +2,8 @@
 
 'pre_norm': x = x + mixer(norm[0](x)); x = x + feed_forward(norm[1](x))  (damendaemon/gpt2.py:47-64).
 'pre_norm_mixer': x = x + mixer(norm[0](x)), a layer without a feed-forward.
+'parallel': y = norm[0](x); x = x + mixer(y) + feed_forward(y): one norm, both read its output, both results are added
+to the float32 stream (by the epilogues of their last products, one after the other).
 """
 from __future__ import annotations
 
@@ -29,3 +31,16 @@ class PreNormMixerOnly:
 
     def forward(self, x, ctx, cache, position):
         return self.mixer.forward(self.norms[0].forward(x), x, ctx, cache, position)
+
+
+@register_arrangement("parallel")
+class ParallelBlock:
+    def __init__(self, spec, norms, mixer, feed_forward):
+        if len(norms) != 1:
+            raise ValueError(f"a parallel block takes one norm, got {len(norms)}")
+        self.spec, self.norms, self.mixer, self.feed_forward = spec, list(norms), mixer, feed_forward
+
+    def forward(self, x, ctx, cache, position):
+        y = self.norms[0].forward(x)
+        x = self.mixer.forward(y, x, ctx, cache, position)
+        return self.feed_forward.forward(y, x, ctx)

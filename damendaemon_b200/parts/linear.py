@@ -42,9 +42,10 @@ def grouped_linear(tensor_cores, a, w, tile_group, tile, out_dtype=None):
     return kernels.gemm_simt_grouped(a, w, tile_group, out_dtype=out_dtype or a.dtype)
 
 
-def grouped_gated_unit(tensor_cores, a, gate_up, tile_group, tile, limit, alpha):
-    """The gated unit over grouped rows: gate_up [groups, 2 * inner, in] holds a group's gate rows, then its up rows.
-    On the tensor cores both products and the unit are one kernel; else a grouped product and the unit's own kernel."""
+def grouped_gated_unit(tensor_cores, a, gate_up, tile_group, tile, limit, alpha, form="clamped_swish"):
+    """The gated unit (form: one of kernels.GATED_FORMS) over grouped rows: gate_up [groups, 2 * inner, in] holds a group's
+    gate rows, then its up rows. On the tensor cores both products and the unit are one kernel; else a grouped product and
+    the unit's own kernel."""
     if tensor_cores:
-        return kernels.gemm_grouped_tcgen05(a, gate_up, tile_group, tile, gated=(limit, alpha))
-    return kernels.gated_unit(kernels.gemm_simt_grouped(a, gate_up, tile_group), limit, alpha)
+        return kernels.gemm_grouped_tcgen05(a, gate_up, tile_group, tile, gated=(limit, alpha, form))
+    return kernels.gated_unit(kernels.gemm_simt_grouped(a, gate_up, tile_group), limit, alpha, form=form)

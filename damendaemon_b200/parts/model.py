@@ -1,7 +1,7 @@
 """A decoder assembled from parts according to a ModelSpec. Architecture-agnostic."""
 from __future__ import annotations
 
-from . import attention, block, embedding, feed_forward, head, norms, positions  # noqa: F401  (register the built-in parts)
+from . import attention, block, embedding, feed_forward, head, norms, positions, retention  # noqa: F401  (register the built-in parts)
 from .registry import ARRANGEMENTS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITIONS, lookup
 
 

@@ -38,7 +38,14 @@ def prompt_key_block(n_heads, kv_heads, head_dim, page_size, dtype):
 def paged_attention(ctx, q, k, v, cache, n_heads, scale, window=None, chunk=None, gate=None, value_dim=None):
     runtime = ctx.runtime
     tune = runtime.attention_tuning
-    if not (q.stride(0) == k.stride(0) == v.stride(0)) or q.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1 or \
+    if (k is None) != (v is None) or (k is None and cache.writable):
+        raise ValueError("keys and values come together; only a mixer that reads another stop's cache brings none")
+    if k is None:
+        # queries only: the keys and values are another stop's, in the cache already
+        if q.stride(1) != 1 or (gate is not None and (gate.stride(0) != q.stride(0) or gate.stride(1) != 1)):
+            q = q.contiguous()
+            gate = None if gate is None else gate.contiguous()
+    elif not (q.stride(0) == k.stride(0) == v.stride(0)) or q.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1 or \
             (gate is not None and (gate.stride(0) != q.stride(0) or gate.stride(1) != 1)):
         # the kernels read q, k and v as row views of one buffer (what a fused projection leaves); a part that made
         # new tensors of some of them (a position encoding that does not rotate in place) gets them packed again

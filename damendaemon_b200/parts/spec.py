@@ -92,6 +92,39 @@ class AttentionSpec:
     chunk: Optional[int] = None       # positions in chunks of this many from the start; nothing is seen across a border
     gate_weight: Optional[str] = None  # [n_heads, width]: a head's output is multiplied by sigmoid(gate . input)
     rotary: object = None             # a position-encoding spec of the mixer's own (applied to its queries and keys)
+    # RMS norm of every query head and every key head over the head's dimensions, before the rotation: the checkpoint
+    # names of the two weights [head_dim] (one weight for all heads of a kind; None for a kind that is not normed)
+    query_norm: Optional[str] = None
+    key_norm: Optional[str] = None
+    head_norm_eps: float = 1e-6
+    # False: the mixer has no key and value projections (qkv_weight names the query projection alone) and reads
+    # the cache of another stop of the run order (RunEntry.cache_of), with its own queries, mask and scale
+    own_keys_values: bool = True
+    # keys kept in the cache where other stops read it through a wider mask than this mixer's own ('all': every key);
+    # None: what the mixer's own window needs
+    keep_window: object = None
+
+
+@dataclass(frozen=True)
+class RetentionSpec:
+    """Linear attention with a fixed decay per head and no softmax: per head S_t = decay * S_(t-1) + k_t v_t^T,
+    o_t = S_t^T q_t, the state S [head_dim, value_dim] float32 per request, from zero. Queries and keys may be rotated
+    (``rotary``); keys are multiplied by ``key_scale`` after the rotation. Every head's o is divided by its root mean
+    square (``norm_eps`` inside the root, no weight), multiplied by silu(W_gate y) and projected by W_out."""
+    kind: str            # 'retention'
+    width: int
+    n_heads: int
+    head_dim: int
+    value_dim: int
+    decay: Tuple[float, ...]       # one per head
+    key_scale: float
+    norm_eps: float
+    query_weight: str    # checkpoint names; matrices [out, in]
+    key_weight: str
+    value_weight: str
+    gate_weight: str
+    out_weight: str
+    rotary: object = None
 
 
 @dataclass(frozen=True)
@@ -109,14 +142,30 @@ class DenseFeedForwardSpec:
 
 @dataclass(frozen=True)
 class GatedUnitSpec:
-    """A small feed-forward with a clamped gate: g = min(W_gate y, limit), u = clamp(W_up y, -limit, limit),
-    output W_down (g * sigmoid(alpha g) * (u + 1)). No biases."""
+    """A small feed-forward of three matrices, W_down (f(W_gate y, W_up y)), no biases. ``activation``:
+    'clamped_swish'  g = min(gate, limit), u = clamp(up, -limit, limit), f = g * sigmoid(alpha g) * (u + 1);
+    'silu'           f = gate * sigmoid(gate) * up;
+    'gelu_tanh'      f = 0.5 gate (1 + tanh(sqrt(2/pi) (gate + 0.044715 gate^3))) * up
+    (limit and alpha belong to the first only)."""
     inner: int
     limit: float
     gate_weight: str
     up_weight: str
     down_weight: str
     alpha: float = 1.702
+    activation: str = "clamped_swish"
+
+
+@dataclass(frozen=True)
+class GatedFeedForwardSpec:
+    """A dense feed-forward that is one gated unit: residual + W_down (f(W_gate y, W_up y))."""
+    kind: str            # 'gated'
+    width: int
+    unit: GatedUnitSpec
+
+    @property
+    def inner(self):
+        return self.unit.inner
 
 
 @dataclass(frozen=True)
@@ -131,6 +180,26 @@ class TableRoutedExpertsSpec:
 
 
 @dataclass(frozen=True)
+class ScoreRoutedExpertsSpec:
+    """Experts chosen per token by a router: z = W_router y in float32, s = ``score``(z) ('sigmoid'); the experts
+    form ``groups`` equal runs of neighbours, a run's worth is the sum of its two largest scores, only experts of the
+    ``keep_groups`` worthiest runs can be chosen; the ``top`` largest eligible scores win. A chosen expert's output is
+    weighted by s * weight_scale (not renormalised). ``shared``: a unit that runs for every token; with
+    ``shared_gate`` (a checkpoint name, [1, width]) its output is multiplied by sigmoid(gate . y)."""
+    kind: str            # 'experts_by_score'
+    width: int
+    top: int
+    router: str          # checkpoint name of W_router [experts, width]
+    experts: Tuple[GatedUnitSpec, ...]       # all of one size and activation
+    groups: int = 1
+    keep_groups: int = 1
+    weight_scale: float = 1.0
+    score: str = "sigmoid"
+    shared: Optional[GatedUnitSpec] = None
+    shared_gate: Optional[str] = None
+
+
+@dataclass(frozen=True)
 class NoFeedForwardSpec:
     kind: str = "none"
 
@@ -139,7 +208,7 @@ class NoFeedForwardSpec:
 class LayerSpec:
     """A layer: a mixer, a feed-forward, as many norms as its arrangement wants, and the arrangement that wires them
     ('pre_norm' takes two norms: before the mixer, before the feed-forward; 'pre_norm_mixer' one norm and no
-    feed-forward)."""
+    feed-forward; 'parallel' one norm whose output both the mixer and the feed-forward read)."""
     arrangement: str
     mixer: object
     feed_forward: object

@@ -51,4 +51,4 @@ def load_config(model_dir):
 
 
 def _load_builtin():
-    from .architectures import bonatar, gpt2  # noqa: F401  (register themselves on import)
+    from .architectures import bonatar, gpt2, zokanex  # noqa: F401  (register themselves on import)
