@@ -341,6 +341,43 @@ DESIGN_KERNEL_PAIRS = [      # (a kernel of the new design, the like kernel of G
 ]
 
 
+ZOKANEX_KERNEL_PAIRS = [     # (a kernel of Zokanex, the like kernel of the closest model, Bonatar) at width 1600, 25 heads of 64
+    ("rmsnorm_m2048", "rmsnorm_m2048"), ("headnorm_m2048", "rotary_m2048"), ("headnorm_m8", "rotary_m8"),
+    ("retention_p2_t1024", "attn_prefill_p2_t1024_masked"), ("retention_p8_t1", "attn_decode_b8_masked"),
+    ("retention_p64_t1", "attn_decode_b64_masked"), ("retfinish_p2_t1024", None), ("retfinish_p8_t1", None),
+    ("gatedact_m2048", None), ("gatedact_m8", None),
+    ("grouped_upsilu_m2048", "grouped_up_m2048"), ("grouped_upsilu_m8", "grouped_up_m8"),
+    ("grouped_score_m2048", "grouped_route_m2048"), ("grouped_score_m8", "grouped_route_m8"),
+]
+CUDA_CORE_FP32_TFLOPS = 148 * 128 * 2 * 1.965e9 / 1e12      # nominal: 148 SMs x 128 lanes x one fused multiply-add a cycle at 1,965 MHz
+
+
+def zokanex_configs(size, layers, vocab=50257):
+    """Bonatar (dense; experts) and Zokanex models whose layers have one size: attention layers with a dense gated
+    unit; retention layers with a dense gated unit; the mix of a served model (attention, a layer on the first one's keys,
+    two retention layers, attention) with experts in every second layer."""
+    z = DESIGN_SIZES[size]
+    out = {k: v for k, v in design_configs(size, layers, vocab).items() if k != "gpt2"}
+    rot = {"dims": 64, "base": 10000.0}
+    attention = {"heads": z["heads"], "kv_heads": z["heads"], "dim": 64, "vdim": 64, "scale": 0.125, "mask": {"size": 1024}, "rot": rot}
+    retention = {"heads": z["heads"], "dim": 64, "vdim": 64, "rot": rot,
+                 "decay": [1.0 - 2.0 ** (-5 - 3 * h / max(1, z["heads"] - 1)) for h in range(z["heads"])]}
+    dense = {"kind": "dense", "ff": z["ff"]}
+    moe = {"kind": "moe", "router": {"experts": z["experts"], "top": z["top"], "scale": 2.5, "groups": {"count": 4, "keep": 2}},
+           "expert": {"ff": z["expert_ff"]}, "shared": {"ff": z["expert_ff"]}}
+
+    def model(entries):
+        return {"architecture": "Zokanex", "vocab": vocab, "width": z["width"], "embedding": {"scale": z["width"] ** 0.5},
+                "norm": {"eps": 1e-6}, "layers": [{"type": t, "mixer": m, "mlp": f} for t, m, f in entries]}
+    out["zokanex_attention_dense"] = model([("attention", attention, dense)] * layers)
+    out["zokanex_retention_dense"] = model([("retention", retention, dense)] * layers)
+    pattern = [("attention", attention, dense), ("attention", dict(attention, kv_from=0), moe), ("retention", retention, dense),
+               ("retention", retention, moe), ("attention", attention, dense), ("retention", retention, moe)]
+    out["zokanex_mixed_experts"] = model([pattern[i % len(pattern)] if i % len(pattern) != 1 else
+                                          ("attention", dict(attention, kv_from=i - 1), moe) for i in range(layers)])
+    return out
+
+
 def design_configs(size, layers, vocab=50257):
     """GPT-2 and two Bonatar models (dense layers only; expert layers only) whose layers have one size."""
     z = DESIGN_SIZES[size]
@@ -357,21 +394,23 @@ def design_configs(size, layers, vocab=50257):
 
 
 def design_bench(args):
-    """``--design bonatar``: prefill and decode throughput of Bonatar beside GPT-2 at equal layer sizes (random
-    bfloat16 weights, a few layers), and each kernel of the new design beside the like kernel of GPT-2, timed in a
+    """``--design bonatar`` (beside GPT-2) or ``--design zokanex`` (beside Bonatar, the closest model): prefill and decode
+    throughput at equal layer sizes (random
+    bfloat16 weights, a few layers), and each kernel of the new design beside the like kernel of the other, timed in a
     chain replayed from a CUDA graph over inputs that rotate through more memory than L2 holds."""
     import torch
     from bench_kernel_cases import time_case
     measured_peaks, peaks_from = peaks()
     hbm, tflops = measured_peaks["hbm_gbs"], measured_peaks["bf16_tflops"]
     layers = args.layers or 6
-    out = {"design": "bonatar", "layers": layers, "dtype": "bf16", "data": "synthetic", "peaks": dict(measured_peaks, source=peaks_from),
+    configs_of, pairs = (zokanex_configs, ZOKANEX_KERNEL_PAIRS) if args.design == "zokanex" else (design_configs, DESIGN_KERNEL_PAIRS)
+    out = {"design": args.design, "layers": layers, "dtype": "bf16", "data": "synthetic", "peaks": dict(measured_peaks, source=peaks_from),
            "sizes": {}, "kernels": [],
            "note": "throughput in tokens a second on one B200, timed on the device; chunks of 1024 positions hold the whole context, "
                    "so both designs attend over the same keys"}
     for size in DESIGN_SIZES:
         row = {}
-        for name, config in design_configs(size, layers).items():
+        for name, config in configs_of(size, layers).items():
             runtime = make_runtime(config, 8)
             vocab = runtime.engine.spec.vocab_size
             ms_prefill = prefill_timed(runtime.engine, vocab)
@@ -385,9 +424,10 @@ def design_bench(args):
 
     def measured(case):
         r = time_case(case, args.case_iters, graph=True)
-        r["roofline_fraction"] = round(max(r["GB_per_s"] / hbm, r["TFLOP_per_s"] / tflops), 4)
+        # a kernel whose sums are float32 on the CUDA cores is held against their nominal peak, not the tensor cores'
+        r["roofline_fraction"] = round(max(r["GB_per_s"] / hbm, r["TFLOP_per_s"] / (CUDA_CORE_FP32_TFLOPS if r["float32_on_cuda_cores"] else tflops)), 4)
         return r
-    for new, like in DESIGN_KERNEL_PAIRS:
+    for new, like in pairs:
         entry = {"new": measured(new), "like": measured(like) if like else None}
         if like:
             entry["fraction_new_over_like"] = round(entry["new"]["roofline_fraction"] / max(entry["like"]["roofline_fraction"], 1e-9), 3)
@@ -446,7 +486,7 @@ def main():
     parser.add_argument("--case-iters", type=int, default=50)
     parser.add_argument("--case-graph", action="store_true", help="time the kernel case as launches replayed from one CUDA graph")
     parser.add_argument("--workload", choices=sorted(WORKLOADS), help="run a scheduler workload instead of the headline bench")
-    parser.add_argument("--design", choices=("bonatar",), help="another design beside GPT-2 at equal layer sizes (prefill, decode, "
+    parser.add_argument("--design", choices=("bonatar", "zokanex"), help="another design beside GPT-2 (zokanex: beside Bonatar) at equal layer sizes (prefill, decode, "
                         "kernel by kernel) instead of the headline bench")
     parser.add_argument("--parity", action="store_true", help="the float32 engine beside the bfloat16 one: on the benchmark's model "
                         "(logit differences, greedy agreement), or with --workload on that workload (the same requests in both)")

@@ -90,6 +90,55 @@ def _rotary_case(rows, dev):
     return run, {"bytes": rows * 2 * H * D * 4, "flops": 6 * rows * H * D}
 
 
+def _head_norm_case(rows, dev):
+    """The heads' RMS norm and the rotation of halves in one pass, on the queries and keys of `rows` tokens (25 + 25
+    heads of 64, all dimensions rotated)."""
+    copies = max(2, min(24, (300 << 20) // (rows * 3 * H * D * 2)))
+    bufs = [torch.randn(rows, 3 * H * D + 32, device=dev).to(torch.bfloat16) for _ in range(copies)]
+    pos = torch.arange(rows, dtype=torch.int32, device=dev) % 1024
+    freqs = (10000.0 ** (-torch.arange(D // 2, dtype=torch.float64) * 2 / D)).float().to(dev)
+    wq, wk = torch.ones(D, device=dev), torch.ones(D, device=dev)
+    run = lambda i: K.head_norm_rotary(bufs[i % copies][:, :H * D], bufs[i % copies][:, H * D:2 * H * D], pos, wq, wk, 1e-6, H, H, D,
+                                       freqs=freqs, interleaved=False)
+    return run, {"bytes": rows * 2 * H * D * 4, "flops": 10 * rows * H * D}
+
+
+def _retention_case(entries, length, dev, finish=False):
+    """Retention of `entries` requests of `length` tokens each in one step (25 heads of 64 by 64, all dimensions
+    rotated): the recurrence over float32 state, or (finish) the read-out's norm and gate. Its sums are float32 on the CUDA
+    cores: 'fp32' tells the roofline to take that peak."""
+    tokens = entries * length
+    copies = max(2, min(24, (300 << 20) // max(1, tokens * 4 * H * D * 2 + entries * H * D * D * 4)))
+    bufs = [torch.randn(tokens, 4 * H * D, device=dev).mul_(0.5).to(torch.bfloat16) for _ in range(copies)]
+    states = [torch.zeros(entries, H, D, D, device=dev) for _ in range(copies)]
+    pos = (torch.arange(tokens, dtype=torch.int32, device=dev) % length) + (0 if length > 1 else 767)
+    start = torch.arange(entries + 1, dtype=torch.int32, device=dev) * length
+    slot = torch.arange(entries, dtype=torch.int32, device=dev)
+    decay = torch.full((H,), 0.99, device=dev)
+    freqs = (10000.0 ** (-torch.arange(D // 2, dtype=torch.float64) * 2 / D)).float().to(dev)
+    o = torch.empty(tokens, H * D, device=dev)
+    out = torch.empty(tokens, H * D, device=dev, dtype=torch.bfloat16)
+    if finish:
+        run = lambda i: K.retention_finish(o, bufs[i % copies][:, 3 * H * D:], H, 1e-6, torch.bfloat16, out=out)
+        return run, {"bytes": tokens * H * D * 8, "flops": 8 * tokens * H * D}
+
+    def run(i):
+        b = bufs[i % copies]
+        K.retention(b[:, :H * D], b[:, H * D:2 * H * D], b[:, 2 * H * D:3 * H * D], pos, start, slot, decay, D ** -0.5, states[i % copies],
+                    freqs=freqs, interleaved=False, out=o)
+    return run, {"bytes": entries * H * D * D * 8 + tokens * H * D * (6 + 4), "flops": 4 * tokens * H * D * D, "fp32": True}
+
+
+def _gated_act_case(rows, dev):
+    """The dense gated unit between its two products: rows of [gate | up] halves (2 x 6400) -> tanh-gelu(gate) * up."""
+    inner = 6400
+    copies = max(2, min(24, (300 << 20) // (rows * 2 * inner * 2)))
+    bufs = [torch.randn(rows, 2 * inner, device=dev).to(torch.bfloat16) for _ in range(copies)]
+    out = torch.empty(rows, inner, device=dev, dtype=torch.bfloat16)
+    run = lambda i: K.gated_unit(bufs[i % copies], 0.0, 1.0, out=out, form="gelu_tanh")
+    return run, {"bytes": rows * inner * 6, "flops": 12 * rows * inner}
+
+
 EXPERTS, TOP, INNER = 16, 2, 1600       # sixteen experts of a quarter of the dense inner width, two per token
 
 
@@ -106,6 +155,19 @@ def _grouped_case(which, tokens, dev):
     pair_row, row_token, tile_group = K.route_by_table(ids, table, EXPERTS, tile)
     rows = K.gather_rows(x, row_token)
     used = int(torch.unique(tile_group[tile_group >= 0]).numel())      # experts whose matrices this step streams
+    if which == "score":
+        # the router's float32 product, the choice within groups, then sorting, gathering and the weighted sum
+        router = torch.randn(EXPERTS + 1, width, device=dev).mul_(0.05).to(torch.bfloat16)
+        stream = torch.zeros(tokens, width, device=dev)
+        y = torch.zeros(rows.shape[0], width, device=dev)
+
+        def run(i):
+            logits = K.gemm_simt(x, router, out_dtype=torch.float32)
+            chosen, weight, _ = K.route_by_score(logits, EXPERTS, TOP, 4, 2, 2.5, gate_col=EXPERTS)
+            pr, rt, tg = K.route_by_table(None, chosen, EXPERTS, tile)
+            K.gather_rows(x, rt)
+            K.combine_rows(y, pr, stream, TOP, 1.0, pair_weight=weight.view(-1))
+        return run, {"bytes": tokens * TOP * width * (2 + 2 + 4) + tokens * width * 10, "flops": tokens * (TOP + 2 * EXPERTS) * width}
     if which == "route":
         stream = torch.zeros(tokens, width, device=dev)
         y = torch.zeros(rows.shape[0], width, device=dev)
@@ -115,10 +177,11 @@ def _grouped_case(which, tokens, dev):
             K.gather_rows(x, rt)
             K.combine_rows(y, pr, stream, TOP, 1.0 / TOP)
         return run, {"bytes": tokens * TOP * width * (2 + 2 + 4) + tokens * width * 8, "flops": tokens * TOP * width}
-    if which == "up":
+    if which in ("up", "upsilu"):
         copies = max(2, min(8, (300 << 20) // (EXPERTS * 2 * INNER * width * 2)))
         weights = [torch.randn(EXPERTS, 2 * INNER, width, device=dev).mul_(0.02).to(torch.bfloat16) for _ in range(copies)]
-        run = lambda i: K.gemm_grouped_tcgen05(rows, weights[i % copies], tile_group, tile, gated=(7.0, 1.702))
+        gated = (0.0, 1.0, "silu") if which == "upsilu" else (7.0, 1.702)
+        run = lambda i: K.gemm_grouped_tcgen05(rows, weights[i % copies], tile_group, tile, gated=gated)
         return run, {"bytes": used * 2 * INNER * width * 2, "flops": 2 * tokens * TOP * 2 * INNER * width}
     hidden = torch.randn(rows.shape[0], INNER, device=dev).to(torch.bfloat16)
     copies = max(2, min(8, (300 << 20) // (EXPERTS * INNER * width * 2)))
@@ -166,8 +229,10 @@ def _prefill_case(prompts, length, dev, kernel="tcgen05", store=False, masked=Fa
 def build(name, device="cuda:0"):
     """name: gemm_<qkv|proj|fc|fc2|head>_m<tokens> | gemm32_<...>_m<tokens> (float32, CUDA cores) | attn_decode_b<batch>[_c<context>] (page streaming) | attn_decode_rows_b<batch>[_c<context>] | attn_prefill_p<prompts>_t<tokens> | attn_prefill | attn_prefill_store (the kernel writes the cache too) | attn_prefill_mma |
     attn_prefill_long (one prompt of 4,096 tokens) | layernorm_m<rows> | rmsnorm_m<rows> | rotary_m<rows> |
-    grouped_<up|down|route>_m<tokens> (sixteen experts, two per token); attention cases take the suffix _masked (a chunked
-    mask and a gate on every head's output)"""
+    grouped_<up|upsilu|down|route|score>_m<tokens> (sixteen experts, two per token; upsilu: the silu form of the unit;
+    score: routing by a router's scores) | headnorm_m<rows> | gatedact_m<rows> | retention_p<requests>_t<tokens> |
+    retfinish_p<requests>_t<tokens>; attention cases take the suffix _masked (a chunked mask and a gate on every head's
+    output)"""
     K.library("core"), K.library("tensor")
     masked = name.endswith("_masked")          # attention cases: with a chunked mask and an output gate
     if masked:
@@ -177,7 +242,15 @@ def build(name, device="cuda:0"):
         return _rmsnorm_case(int(name[len("rmsnorm_m"):]), device)
     if name.startswith("rotary_m"):
         return _rotary_case(int(name[len("rotary_m"):]), device)
-    if parts[0] == "grouped" and len(parts) == 3 and parts[1] in ("up", "down", "route") and parts[2][0] == "m":
+    if name.startswith("headnorm_m"):
+        return _head_norm_case(int(name[len("headnorm_m"):]), device)
+    if name.startswith("gatedact_m"):
+        return _gated_act_case(int(name[len("gatedact_m"):]), device)
+    if name.startswith("retention_p") or name.startswith("retfinish_p"):
+        # retention_p<requests>_t<tokens of each>: prompts; _t1: a decode step of that many requests
+        entries, tokens = name.split("_p")[1].split("_t")
+        return _retention_case(int(entries), int(tokens), device, finish=name.startswith("retfinish"))
+    if parts[0] == "grouped" and len(parts) == 3 and parts[1] in ("up", "upsilu", "down", "route", "score") and parts[2][0] == "m":
         return _grouped_case(parts[1], int(parts[2][1:]), device)
     if parts[0] == "gemm" and len(parts) == 3 and parts[1] in SHAPES and parts[2][0] == "m":
         return _gemm_case(parts[1], int(parts[2][1:]), device)
@@ -234,4 +307,5 @@ def time_case(name, iters=50, device="cuda:0", graph=False):
     torch.cuda.synchronize()
     us = start.elapsed_time(stop) * 1000.0 / iters
     return {"case": name, "us_per_launch": round(us, 2), "GB_per_s": round(work["bytes"] / us / 1e3, 1),
-            "TFLOP_per_s": round(work["flops"] / us / 1e6, 1), "iters": iters, "graph": bool(graph)}
+            "TFLOP_per_s": round(work["flops"] / us / 1e6, 1), "iters": iters, "graph": bool(graph),
+            "float32_on_cuda_cores": bool(work.get("fp32", False))}
