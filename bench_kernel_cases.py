@@ -110,7 +110,7 @@ def _retention_case(entries, length, dev, finish=False):
     tokens = entries * length
     copies = max(2, min(24, (300 << 20) // max(1, tokens * 4 * H * D * 2 + entries * H * D * D * 4)))
     bufs = [torch.randn(tokens, 4 * H * D, device=dev).mul_(0.5).to(torch.bfloat16) for _ in range(copies)]
-    states = [torch.zeros(entries, H, D, D, device=dev) for _ in range(copies)]
+    states = [torch.zeros(entries, *K.retention_state_shape(H, D, D), device=dev) for _ in range(copies)]
     pos = (torch.arange(tokens, dtype=torch.int32, device=dev) % length) + (0 if length > 1 else 767)
     start = torch.arange(entries + 1, dtype=torch.int32, device=dev) * length
     slot = torch.arange(entries, dtype=torch.int32, device=dev)
@@ -125,7 +125,7 @@ def _retention_case(entries, length, dev, finish=False):
     def run(i):
         b = bufs[i % copies]
         K.retention(b[:, :H * D], b[:, H * D:2 * H * D], b[:, 2 * H * D:3 * H * D], pos, start, slot, decay, D ** -0.5, states[i % copies],
-                    freqs=freqs, interleaved=False, out=o)
+                    D, D, freqs=freqs, interleaved=False, out=o)
     return run, {"bytes": entries * H * D * D * 8 + tokens * H * D * (6 + 4), "flops": 4 * tokens * H * D * D, "fp32": True}
 
 
@@ -156,14 +156,13 @@ def _grouped_case(which, tokens, dev):
     rows = K.gather_rows(x, row_token)
     used = int(torch.unique(tile_group[tile_group >= 0]).numel())      # experts whose matrices this step streams
     if which == "score":
-        # the router's float32 product, the choice within groups, then sorting, gathering and the weighted sum
+        # the router's logits and the choice within groups (one kernel), then sorting, gathering and the weighted sum
         router = torch.randn(EXPERTS + 1, width, device=dev).mul_(0.05).to(torch.bfloat16)
         stream = torch.zeros(tokens, width, device=dev)
         y = torch.zeros(rows.shape[0], width, device=dev)
 
         def run(i):
-            logits = K.gemm_simt(x, router, out_dtype=torch.float32)
-            chosen, weight, _ = K.route_by_score(logits, EXPERTS, TOP, 4, 2, 2.5, gate_col=EXPERTS)
+            chosen, weight, _ = K.route_by_score(x, router, EXPERTS, TOP, 4, 2, 2.5, shared_gate=True)
             pr, rt, tg = K.route_by_table(None, chosen, EXPERTS, tile)
             K.gather_rows(x, rt)
             K.combine_rows(y, pr, stream, TOP, 1.0, pair_weight=weight.view(-1))

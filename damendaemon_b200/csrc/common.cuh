@@ -75,6 +75,21 @@ __device__ __forceinline__ void dd_launch_dependents() { asm volatile("griddepco
 
 extern int dd_pdl_enabled;      // errors.cu; switched by dd_set_pdl()
 
+// A launch in plain stream order, whatever dd_pdl_enabled says: for a kernel of few long-running blocks, which must be
+// dealt out over an empty GPU (started early, its blocks go wherever the kernel before has just freed room, several to
+// an SM while others stay empty, and stay there).
+template <typename... KArgs, typename... Args>
+static inline cudaError_t dd_launch_in_order(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                                             Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    config.numAttrs = 0;
+    return cudaLaunchKernelEx(&config, kernel, static_cast<KArgs>(args)...);
+}
+
 template <typename... KArgs, typename... Args>
 static inline cudaError_t dd_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                                     Args... args) {

@@ -8,7 +8,8 @@
 // value is never rounded to the storage type before it is rotated. Sum of squares, root, angle, cosine and sine are
 // float32 whatever the storage type.
 //
-// A warp owns one (token, head). k may be null with k_heads == 0: a mixer that reads another layer's keys has
+// A block owns a token and a share of its heads: it computes the token's cosines and sines once (they serve every head),
+// then each of its warps takes heads in turn. k may be null with k_heads == 0: a mixer that reads another layer's keys has
 // queries only.
 #include "common.cuh"
 
@@ -19,43 +20,47 @@ template <typename T>
 __global__ void __launch_bounds__(WARPS * 32)
 head_norm_rotary_kernel(T* __restrict__ q, T* __restrict__ k, int stride, const int* __restrict__ positions,
                         const float* __restrict__ freqs, const float* __restrict__ q_weight,
-                        const float* __restrict__ k_weight, float eps, int n_tokens, int q_heads, int k_heads, int head_dim,
-                        int n_pairs, int interleaved) {
-    extern __shared__ float staged[];             // [WARPS][head_dim]
+                        const float* __restrict__ k_weight, float eps, int q_heads, int k_heads, int head_dim,
+                        int n_pairs, int interleaved, int heads_per_block) {
+    extern __shared__ float staged[];             // [n_pairs] cosines, [n_pairs] sines, [WARPS][head_dim] a head per warp
+    float* cosines = staged;
+    float* sines = staged + n_pairs;
     dd_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int heads = q_heads + k_heads;
-    const long long item = (long long)blockIdx.x * WARPS + warp;
-    const bool live = item < (long long)n_tokens * heads;
-    const int t = live ? (int)(item / heads) : 0, h = live ? (int)(item % heads) : 0;
+    const int t = blockIdx.x;
     const float p = (float)positions[t];          // positions are the step's input, not the projection's output
+    for (int i = threadIdx.x; i < n_pairs; i += WARPS * 32) sincosf(p * freqs[i], &sines[i], &cosines[i]);
+    __syncthreads();
     dd_grid_wait();
-    if (!live) return;
-    T* head = h < q_heads ? q + (size_t)t * stride + (size_t)h * head_dim : k + (size_t)t * stride + (size_t)(h - q_heads) * head_dim;
-    const float* w = h < q_heads ? q_weight : k_weight;
-    float* x = staged + warp * head_dim;
-    float sq = 0.f;
-    for (int c = lane; c < head_dim; c += 32) {
-        const float v = dd_to_f32(head[c]);
-        x[c] = v;
-        sq += v * v;
+    float* x = staged + 2 * n_pairs + warp * head_dim;
+    const int heads = q_heads + k_heads;
+    const int h_end = min(heads, (int)(blockIdx.y + 1) * heads_per_block);
+    for (int h = blockIdx.y * heads_per_block + warp; h < h_end; h += WARPS) {
+        T* head = h < q_heads ? q + (size_t)t * stride + (size_t)h * head_dim : k + (size_t)t * stride + (size_t)(h - q_heads) * head_dim;
+        const float* w = h < q_heads ? q_weight : k_weight;
+        float sq = 0.f;
+        for (int c = lane; c < head_dim; c += 32) {
+            const float v = dd_to_f32(head[c]);
+            x[c] = v;
+            sq += v * v;
+        }
+        sq = dd_warp_sum(sq);
+        if (w) {
+            const float r = 1.0f / sqrtf(sq / (float)head_dim + eps);
+            for (int c = lane; c < head_dim; c += 32) x[c] = x[c] * r * w[c];
+        }
+        __syncwarp();
+        for (int i = lane; i < n_pairs; i += 32) {
+            const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + n_pairs;
+            const float cs = cosines[i], sn = sines[i];
+            const float a = x[ia], b = x[ib];
+            head[ia] = dd_from_f32<T>(a * cs - b * sn);
+            head[ib] = dd_from_f32<T>(b * cs + a * sn);
+        }
+        if (w)
+            for (int c = 2 * n_pairs + lane; c < head_dim; c += 32) head[c] = dd_from_f32<T>(x[c]);
+        __syncwarp();                             // the next head of this warp overwrites x
     }
-    sq = dd_warp_sum(sq);
-    if (w) {
-        const float r = 1.0f / sqrtf(sq / (float)head_dim + eps);
-        for (int c = lane; c < head_dim; c += 32) x[c] = x[c] * r * w[c];
-    }
-    __syncwarp();
-    for (int i = lane; i < n_pairs; i += 32) {
-        const int ia = interleaved ? 2 * i : i, ib = interleaved ? 2 * i + 1 : i + n_pairs;
-        float sn, cs;
-        sincosf(p * freqs[i], &sn, &cs);
-        const float a = x[ia], b = x[ib];
-        head[ia] = dd_from_f32<T>(a * cs - b * sn);
-        head[ib] = dd_from_f32<T>(b * cs + a * sn);
-    }
-    if (w)
-        for (int c = 2 * n_pairs + lane; c < head_dim; c += 32) head[c] = dd_from_f32<T>(x[c]);
 }
 }  // namespace
 
@@ -71,15 +76,21 @@ DD_API int dd_head_norm_rotary(void* q, void* k, int stride, const int* position
     if ((k_heads > 0 && !k) || (q_heads > 0 && !q) || (n_pairs > 0 && !freqs))
         return dd_fail("dd_head_norm_rotary: a null pointer for heads or frequencies that are wanted");
     cudaStream_t s = (cudaStream_t)stream;
-    const int grid = dd_ceil_div((long long)n_tokens * (q_heads + k_heads), WARPS);
-    const size_t smem = (size_t)WARPS * head_dim * sizeof(float);
+    // a token's heads are shared out over as many blocks as give the GPU two blocks an SM (at most a block per WARPS heads)
+    const int heads = q_heads + k_heads;
+    int groups = dd_ceil_div(296, n_tokens);
+    if (groups > dd_ceil_div(heads, WARPS)) groups = dd_ceil_div(heads, WARPS);
+    if (groups < 1) groups = 1;
+    const int heads_per_block = dd_ceil_div(heads, groups);
+    const dim3 grid(n_tokens, dd_ceil_div(heads, heads_per_block));
+    const size_t smem = ((size_t)WARPS * head_dim + 2 * (size_t)n_pairs) * sizeof(float);
     if (dtype == DD_F32)
-        dd_launch(head_norm_rotary_kernel<float>, dim3(grid), dim3(WARPS * 32), smem, s, (float*)q, (float*)k, stride, positions,
-                  freqs, q_weight, k_weight, eps, n_tokens, q_heads, k_heads, head_dim, n_pairs, interleaved);
+        dd_launch(head_norm_rotary_kernel<float>, grid, dim3(WARPS * 32), smem, s, (float*)q, (float*)k, stride, positions,
+                  freqs, q_weight, k_weight, eps, q_heads, k_heads, head_dim, n_pairs, interleaved, heads_per_block);
     else if (dtype == DD_BF16)
-        dd_launch(head_norm_rotary_kernel<__nv_bfloat16>, dim3(grid), dim3(WARPS * 32), smem, s, (__nv_bfloat16*)q,
-                  (__nv_bfloat16*)k, stride, positions, freqs, q_weight, k_weight, eps, n_tokens, q_heads, k_heads, head_dim,
-                  n_pairs, interleaved);
+        dd_launch(head_norm_rotary_kernel<__nv_bfloat16>, grid, dim3(WARPS * 32), smem, s, (__nv_bfloat16*)q,
+                  (__nv_bfloat16*)k, stride, positions, freqs, q_weight, k_weight, eps, q_heads, k_heads, head_dim,
+                  n_pairs, interleaved, heads_per_block);
     else
         return dd_fail("dd_head_norm_rotary: unknown dtype %d", dtype);
     return dd_check_launch("dd_head_norm_rotary");

@@ -8,8 +8,8 @@
 //                       (the token of a row, -1 for a row of padding), tile_group [rows / tile]
 //   dd_gather_rows      x [N, width] -> sorted rows (a row of padding is zeroed)
 //                       (ids null: token t reads row t of the table, which then holds the step's own choices)
-//   dd_route_by_score   router logits [N, >= E] -> the K experts of every token by score within the worthiest groups,
-//                       their weights, and the gate of a shared unit
+//   dd_route_by_score   normed rows [N, width] and the router's matrix -> float32 logits, then the K experts of every token
+//                       by score within the worthiest groups, their weights, and the gate of a shared unit
 //   dd_gated_unit       rows of [gate | up] halves -> y = f(gate, up) in float32 (dd_gated_value in common.cuh: the
 //                       clamped form g * sigmoid(alpha g) * (u + 1), silu(gate) * up, or tanh-gelu(gate) * up),
 //                       optionally times a number per row
@@ -95,12 +95,38 @@ route_by_table_kernel(const int* __restrict__ ids, const int* __restrict__ table
 }
 
 
-// One warp per token. scores of E experts in shared memory; a run's worth by the lanes (a run each); the worthiest
-// runs and then the best experts by repeated arg-max over the warp, the lowest index winning a tie.
+// A 16-byte piece of a row as float32 values (exact for both storage types).
+template <typename T> struct RoutePiece;
+template <> struct RoutePiece<float> {
+    static constexpr int N = 4;
+    __device__ static void load(const float* p, float* out) {
+        const float4 v = *reinterpret_cast<const float4*>(p);
+        out[0] = v.x; out[1] = v.y; out[2] = v.z; out[3] = v.w;
+    }
+};
+template <> struct RoutePiece<__nv_bfloat16> {
+    static constexpr int N = 8;
+    __device__ static void load(const __nv_bfloat16* p, float* out) {
+        const uint4 v = *reinterpret_cast<const uint4*>(p);
+        const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            out[2 * i] = __uint_as_float(w[i] << 16);
+            out[2 * i + 1] = __uint_as_float(w[i] & 0xffff0000u);
+        }
+    }
+};
+
+// One warp per token. First the router's logits, float32 sums of exact products: a lane sums the pieces lane, lane + 32,
+// ... of the row against eight router rows at a time (the token's row comes from L1 again for the next eight), the
+// lanes' sums are added in a fixed tree, so a token's logits do not depend on what else is in the step. Then the
+// scores of the E experts in shared memory; a run's worth by the lanes (a run each); the worthiest runs and then the
+// best experts by repeated arg-max over the warp, the lowest index winning a tie.
+template <typename T>
 __global__ void __launch_bounds__(128)
-route_by_score_kernel(const float* __restrict__ logits, int ld, int n_tokens, int n_experts, int top, int groups, int keep,
-                      float weight_scale, int gate_col, int* __restrict__ chosen, float* __restrict__ pair_weight,
-                      float* __restrict__ shared_scale) {
+route_by_score_kernel(const T* __restrict__ y, int ldy, const T* __restrict__ router, int ldr, int width, int n_tokens,
+                      int n_experts, int top, int groups, int keep, float weight_scale, int gate_row,
+                      int* __restrict__ chosen, float* __restrict__ pair_weight, float* __restrict__ shared_scale) {
     extern __shared__ float route_smem[];        // per warp: [E] scores, [groups] worths
     dd_launch_dependents();
     dd_grid_wait();
@@ -109,14 +135,49 @@ route_by_score_kernel(const float* __restrict__ logits, int ld, int n_tokens, in
     if (t >= n_tokens) return;
     float* score = route_smem + warp * (n_experts + groups);
     float* worth = score + n_experts;
-    const float* z = logits + (size_t)t * ld;
-    for (int e = lane; e < n_experts; e += 32) score[e] = 1.0f / (1.0f + expf(-z[e]));
-    if (lane == 0 && shared_scale) shared_scale[t] = gate_col >= 0 ? 1.0f / (1.0f + expf(-z[gate_col])) : 1.0f;
+    const T* x = y + (size_t)t * ldy;
+    constexpr int V = RoutePiece<T>::N, ROWS = 8;
+    const bool wide = width % V == 0 && ldy % V == 0 && ldr % V == 0 && !(((uintptr_t)y | (uintptr_t)router) & 15);
+    const int n_rows = n_experts + (gate_row >= 0 ? 1 : 0);          // the shared unit's gate vector is one more row
+    float gate_logit = 0.f;
+    for (int e0 = 0; e0 < n_rows; e0 += ROWS) {
+        float acc[ROWS];
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j) acc[j] = 0.f;
+        if (wide) {
+            for (int c = lane * V; c < width; c += 32 * V) {
+                float xv[V];
+                RoutePiece<T>::load(x + c, xv);
+#pragma unroll
+                for (int j = 0; j < ROWS; ++j) {
+                    if (e0 + j >= n_rows) break;
+                    float wv[V];
+                    RoutePiece<T>::load(router + (size_t)(e0 + j) * ldr + c, wv);
+#pragma unroll
+                    for (int i = 0; i < V; ++i) acc[j] = fmaf(xv[i], wv[i], acc[j]);
+                }
+            }
+        } else {
+            for (int c = lane; c < width; c += 32) {
+                const float xv = dd_to_f32(x[c]);
+#pragma unroll
+                for (int j = 0; j < ROWS; ++j)
+                    if (e0 + j < n_rows) acc[j] = fmaf(xv, dd_to_f32(router[(size_t)(e0 + j) * ldr + c]), acc[j]);
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < ROWS; ++j) {
+            const float z = dd_warp_sum(acc[j]);
+            if (e0 + j < n_experts) { if (lane == 0) score[e0 + j] = 1.0f / (1.0f + expf(-z)); }
+            else if (e0 + j == gate_row) gate_logit = z;
+        }
+    }
+    if (lane == 0 && shared_scale) shared_scale[t] = gate_row >= 0 ? 1.0f / (1.0f + expf(-gate_logit)) : 1.0f;
     __syncwarp();
     const int per = n_experts / groups;
     if (groups > 1) {
         for (int g = lane; g < groups; g += 32) {
-            float best = -1.f, second = -1.f;            // scores lie in (0, 1)
+            float best = -1.f, second = -1.f;            // scores lie in [0, 1]
             for (int i = 0; i < per; ++i) {
                 const float s = score[g * per + i];
                 if (s > best) { second = best; best = s; }
@@ -277,22 +338,32 @@ DD_API int dd_route_by_table(const int* ids, const int* table, int n_tokens, int
     return dd_check_launch("dd_route_by_table");
 }
 
-// logits: float32 [n_tokens] rows of ld values, the first n_experts the router's; score = sigmoid(logit). The experts
-// form `groups` equal runs of neighbours, a run's worth is the sum of its two largest scores (of its one), only the `keep`
-// worthiest runs stay eligible; the `top` largest eligible scores win. chosen: int32 [n_tokens, top] by falling score
-// (-1 where fewer were eligible), pair_weight: float32 [n_tokens, top] = score * weight_scale. shared_scale (or null):
-// float32 [n_tokens] = sigmoid(logits[t][gate_col]), 1 with gate_col < 0.
-DD_API int dd_route_by_score(const float* logits, int ld, int n_tokens, int n_experts, int top, int groups, int keep,
-                             float weight_scale, int gate_col, int* chosen, float* pair_weight, float* shared_scale,
-                             void* stream) {
+// y: [n_tokens] rows of ldy elements, `width` of them the token's normed row; router: [n_experts (+ 1)] rows of ldr
+// elements (the same storage type). logit = y . router row, float32 sums of exact products; score = sigmoid(logit). The
+// experts form `groups` equal runs of neighbours, a run's worth is the sum of its two largest scores (of its one), only the
+// `keep` worthiest runs stay eligible; the `top` largest eligible scores win. chosen: int32 [n_tokens, top] by falling
+// score (-1 where fewer were eligible), pair_weight: float32 [n_tokens, top] = score * weight_scale. shared_scale (or
+// null): float32 [n_tokens] = sigmoid(y . router row gate_row), 1 with gate_row < 0 (gate_row is n_experts or negative).
+DD_API int dd_route_by_score(const void* y, int ldy, const void* router, int ldr, int width, int n_tokens, int n_experts,
+                             int top, int groups, int keep, float weight_scale, int gate_row, int* chosen,
+                             float* pair_weight, float* shared_scale, int dtype, void* stream) {
     if (n_tokens <= 0) return 0;
     if (n_experts <= 0 || top <= 0 || top > n_experts || groups <= 0 || n_experts % groups || keep <= 0 || keep > groups ||
-        gate_col >= ld || n_experts > ld)
-        return dd_fail("dd_route_by_score: %d of %d experts in %d groups of which %d stay, rows of %d", top, n_experts, groups, keep, ld);
+        (gate_row >= 0 && gate_row != n_experts) || width <= 0)
+        return dd_fail("dd_route_by_score: %d of %d experts in %d groups of which %d stay, gate row %d", top, n_experts, groups, keep, gate_row);
     const size_t smem = 4 * (size_t)(n_experts + groups) * sizeof(float);
     if (smem > 48 * 1024) return dd_fail("dd_route_by_score: %d experts are more than a warp's shared memory holds", n_experts);
-    dd_launch(route_by_score_kernel, dim3(dd_ceil_div(n_tokens, 4)), dim3(128), smem, (cudaStream_t)stream, logits, ld, n_tokens,
-              n_experts, top, groups, keep, weight_scale, gate_col, chosen, pair_weight, shared_scale);
+    cudaStream_t s = (cudaStream_t)stream;
+    const dim3 grid(dd_ceil_div(n_tokens, 4));
+    if (dtype == DD_F32)
+        dd_launch(route_by_score_kernel<float>, grid, dim3(128), smem, s, (const float*)y, ldy, (const float*)router, ldr, width,
+                  n_tokens, n_experts, top, groups, keep, weight_scale, gate_row, chosen, pair_weight, shared_scale);
+    else if (dtype == DD_BF16)
+        dd_launch(route_by_score_kernel<__nv_bfloat16>, grid, dim3(128), smem, s, (const __nv_bfloat16*)y, ldy,
+                  (const __nv_bfloat16*)router, ldr, width, n_tokens, n_experts, top, groups, keep, weight_scale, gate_row, chosen,
+                  pair_weight, shared_scale);
+    else
+        return dd_fail("dd_route_by_score: unknown dtype %d", dtype);
     return dd_check_launch("dd_route_by_score");
 }
 

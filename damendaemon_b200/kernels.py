@@ -38,10 +38,10 @@ _SIGNATURES = {
         "dd_gather_rows": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_void],
         "dd_gated_unit": [_c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_float, _c_float, _c_int, _c_void, _c_int, _c_void],
         "dd_combine_rows": [_c_void, _c_void, _c_void, _c_int, _c_int, _c_int, _c_float, _c_void, _c_void],
-        "dd_route_by_score": [_c_void] + [_c_int] * 6 + [_c_float, _c_int, _c_void, _c_void, _c_void, _c_void],
+        "dd_route_by_score": [_c_void, _c_int, _c_void, _c_int] + [_c_int] * 6 + [_c_float, _c_int, _c_void, _c_void, _c_void, _c_int, _c_void],
         "dd_head_norm_rotary": [_c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_void, _c_float] + [_c_int] * 7 + [_c_void],
         "dd_retention": [_c_void, _c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_void,
-                         _c_float, _c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void],
+                         _c_float, _c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_int, _c_void, _c_void, _c_int, _c_void],
         "dd_retention_finish": [_c_void, _c_void, _c_int, _c_void, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_void],
         "dd_gemm_simt": [_c_void, _c_int, _c_void, _c_int, _c_void, _c_void, _c_int, _c_void, _c_int] + [_c_int] * 6 + [_c_void],
         "dd_kv_store": [_c_void, _c_void, _c_int, _c_void, _c_void, _c_void, _c_int, _c_void] + [_c_int] * 7 + [_c_void, _c_void],
@@ -314,27 +314,42 @@ def head_norm_rotary(q, k, positions, q_weight, k_weight, eps, q_heads, k_heads,
     return q, k
 
 
-def retention(q, k, v, positions, entry_start, entry_slot, decay, key_scale, state, freqs=None, interleaved=True, out=None):
+def retention_state_shape(heads, head_dim, value_dim):
+    """Shape of one request's retention state (float32): per head the columns of S one after the other, each padded to a
+    multiple of four rows (a thread of the kernel holds four rows as one 16-byte piece); zeros for a new request."""
+    if not 0 < head_dim <= 256 or value_dim <= 0:
+        raise KernelError(f"retention: heads of {head_dim} by {value_dim} are not supported (keys of at most 256)")
+    return (int(heads), int(value_dim), -(-int(head_dim) // 4) * 4)
+
+
+def retention(q, k, v, positions, entry_start, entry_slot, decay, key_scale, state, head_dim, value_dim, freqs=None,
+              interleaved=True, out=None):
     """The retention recurrence of a step: per entry (rows entry_start[e] .. entry_start[e+1]) and head, from the
-    state in row entry_slot[e] of ``state`` (float32 [slots, heads, dv, dk], read and written), token by token:
-    S = decay * S + k' v^T, o = S^T q', with q', k' rotated by position * freqs (None: not rotated) and k' times
-    key_scale. q, k [N, heads*dk], v [N, heads*dv]: row views of one buffer. Returns o float32 [N, heads*dv]."""
-    n_slots, heads, dv, dk = state.shape
+    state in row entry_slot[e] of ``state`` (float32 [slots, *retention_state_shape(heads, head_dim, value_dim)], read and
+    written), token by token: S = decay * S + k' v^T, o = S^T q', with q', k' rotated by position * freqs (None: not
+    rotated) and k' times key_scale. q, k [N, heads*head_dim], v [N, heads*value_dim]: row views of one buffer. Returns o
+    float32 [N, heads*value_dim]."""
+    n_slots, heads = state.shape[0], state.shape[1]
+    dk, dv = int(head_dim), int(value_dim)
     if not (q.stride(0) == k.stride(0) == v.stride(0)) or q.stride(1) != 1 or k.stride(1) != 1 or v.stride(1) != 1 or \
             not (q.dtype == k.dtype == v.dtype):
         raise KernelError("retention: q, k and v must be row views of one buffer")
     if q.shape[1] != heads * dk or k.shape[1] != heads * dk or v.shape[1] != heads * dv or state.dtype != torch.float32 or \
-            not state.is_contiguous() or decay.numel() != heads:
+            not state.is_contiguous() or decay.numel() != heads or tuple(state.shape[1:]) != retention_state_shape(heads, dk, dv):
         raise KernelError("retention: shapes do not fit the state")
-    n = q.shape[0]
+    n, n_entries = q.shape[0], entry_slot.numel()
     if out is None:
         out = torch.empty((n, heads * dv), dtype=torch.float32, device=q.device)
+    # a step with portions: rotated q and k and v as float32 rows, written once for all the blocks of the recurrence
+    scratch = None
+    if n > n_entries:
+        scratch = torch.empty((n * heads * (2 * (-(-dk // 4) * 4) + -(-dv // 4) * 4),), dtype=torch.float32, device=q.device)
     _call(library("core"), "dd_retention", _ptr(q, "q"), _ptr(k, "k"), _ptr(v, "v"), q.stride(0),
           _ptr(positions, "positions", torch.int32), _ptr(entry_start, "entry_start", torch.int32),
           _ptr(entry_slot, "entry_slot", torch.int32), entry_slot.numel(), _ptr(freqs, "freqs", torch.float32),
           0 if freqs is None else freqs.numel(), 1 if interleaved else 0, _ptr(decay, "decay", torch.float32), float(key_scale),
           _ptr(state, "state"), n_slots, _ptr(out, "out", torch.float32), heads, dk, dv, _dt(q.dtype),
-          _ptr(error_flag(q.device)), _stream())
+          _ptr(error_flag(q.device)), _stream(), n, _ptr(scratch), n_kernels=2 if scratch is not None else 1)
     return out
 
 
@@ -447,19 +462,23 @@ def route_by_table(ids, table, n_experts, tile):
     return pair_row, row_token, tile_group
 
 
-def route_by_score(logits, n_experts, top, groups=1, keep=1, weight_scale=1.0, gate_col=None):
-    """Router logits float32 [N, >= n_experts] -> (chosen int32 [N, top], pair_weight float32 [N, top], shared_scale
-    float32 [N] or None). score = sigmoid(logit); the experts form ``groups`` equal runs of neighbours, a run's worth is
-    the sum of its two largest scores, only the ``keep`` worthiest runs stay eligible; the ``top`` largest eligible
-    scores win, each weighing score * weight_scale. gate_col: the column of ``logits`` whose sigmoid is a shared
-    unit's gate."""
-    _rows(logits, "logits")
-    n = logits.shape[0]
-    chosen = torch.empty((n, top), dtype=torch.int32, device=logits.device)
-    weight = torch.empty((n, top), dtype=torch.float32, device=logits.device)
-    shared = None if gate_col is None else torch.empty((n,), dtype=torch.float32, device=logits.device)
-    _call(library("core"), "dd_route_by_score", _ptr(logits, "logits", torch.float32), logits.stride(0), n, n_experts, top, groups,
-          keep, float(weight_scale), -1 if gate_col is None else int(gate_col), _ptr(chosen), _ptr(weight), _ptr(shared), _stream())
+def route_by_score(y, router, n_experts, top, groups=1, keep=1, weight_scale=1.0, shared_gate=False):
+    """Normed rows y [N, width] and the router's matrix [n_experts (+ 1), width] (one storage type) -> (chosen int32
+    [N, top], pair_weight float32 [N, top], shared_scale float32 [N] or None). logit = y . router row as float32 sums of
+    exact products, score = sigmoid(logit); the experts form ``groups`` equal runs of neighbours, a run's worth is the sum
+    of its two largest scores, only the ``keep`` worthiest runs stay eligible; the ``top`` largest eligible scores win, each
+    weighing score * weight_scale. shared_gate: the router's last row is a shared unit's gate vector, whose sigmoid is
+    returned as shared_scale."""
+    _rows(y, "y"), _rows(router, "router")
+    n, width = y.shape
+    if router.shape != (n_experts + (1 if shared_gate else 0), width) or router.dtype != y.dtype:
+        raise KernelError(f"route_by_score: router {tuple(router.shape)} {router.dtype} does not fit {n_experts} experts over y {tuple(y.shape)} {y.dtype}")
+    chosen = torch.empty((n, top), dtype=torch.int32, device=y.device)
+    weight = torch.empty((n, top), dtype=torch.float32, device=y.device)
+    shared = torch.empty((n,), dtype=torch.float32, device=y.device) if shared_gate else None
+    _call(library("core"), "dd_route_by_score", _ptr(y, "y"), y.stride(0), _ptr(router, "router"), router.stride(0), width, n,
+          n_experts, top, groups, keep, float(weight_scale), n_experts if shared_gate else -1, _ptr(chosen), _ptr(weight),
+          _ptr(shared), _dt(y.dtype), _stream())
     return chosen, weight, shared
 
 

@@ -158,8 +158,9 @@ class GatedFeedForward(FeedForward):
 class ScoreRoutedExperts(FeedForward):
     """out = residual + sum over a token's chosen experts of weight_e * unit_e(y) + gate * shared(y).
 
-    The router's logits are a float32 product (its matrix and, as one more row, the shared unit's gate vector); one
-    kernel turns a token's logits into its experts, their weights and the shared unit's gate (kernels.route_by_score).
+    One kernel (kernels.route_by_score, a warp a token) computes the router's logits as float32 sums (its matrix and, as
+    one more row, the shared unit's gate vector) and turns them into the token's experts, their weights and the shared
+    unit's gate.
     From there on the step is that of experts chosen by a table: the (token, choice) pairs sorted by expert on the
     device, the normed rows gathered in that order, two grouped products (on the tensor cores the first with the gated
     unit in its epilogue), and each token's rows added, weighted, in the order of its choices, into the float32 stream.
@@ -219,10 +220,9 @@ class ScoreRoutedExperts(FeedForward):
     def forward(self, y, residual, ctx):
         s, rt = self.spec, self.runtime
         unit, E = s.experts[0], len(s.experts)
-        # float32 sums of exact products, whatever the storage type of y and the router's rows
-        logits = kernels.gemm_simt(y, self.router, out_dtype=torch.float32)
-        chosen, pair_weight, shared_gate = kernels.route_by_score(logits, E, s.top, s.groups, s.keep_groups, s.weight_scale,
-                                                                  gate_col=E if s.shared_gate else None)
+        # the router's logits (float32 sums of exact products, whatever the storage type) and the choice, in one kernel
+        chosen, pair_weight, shared_gate = kernels.route_by_score(y, self.router, E, s.top, s.groups, s.keep_groups, s.weight_scale,
+                                                                  shared_gate=bool(s.shared_gate))
         if self.shared is not None:
             hidden = kernels.gated_unit(linear(rt, y, self.shared[0]), s.shared.limit, s.shared.alpha, form=s.shared.activation,
                                         row_scale=shared_gate)

@@ -55,8 +55,8 @@ class Retention(Mixer):
 
     @staticmethod
     def cache_needs(spec):
-        # a column of the state (the head_dim values one output column reads) lies together
-        return [RequestState((spec.n_heads, spec.value_dim, spec.head_dim), "float32")]
+        # the state lies as the kernel's warps hold it, so that they read and write whole lines
+        return [RequestState(kernels.retention_state_shape(spec.n_heads, spec.head_dim, spec.value_dim), "float32")]
 
     def forward(self, y, residual, ctx, cache, position):
         s, a, b = self.spec, self.qk_width, self.v_width
@@ -65,7 +65,7 @@ class Retention(Mixer):
         proj = linear(self.runtime, y, self.proj_w)
         q, k, v, gate = proj[:, :a], proj[:, a:2 * a], proj[:, 2 * a:2 * a + b], proj[:, 2 * a + b:2 * a + 2 * b]
         o = kernels.retention(q, k, v, ctx.positions, ctx.entry_start, ctx.entry_slot, self.decay, s.key_scale, cache.state,
-                              freqs=None if self.rotary is None else self.rotary.freqs,
+                              s.head_dim, s.value_dim, freqs=None if self.rotary is None else self.rotary.freqs,
                               interleaved=True if self.rotary is None else self.rotary.spec.interleaved)
         mixed = kernels.retention_finish(o, gate, s.n_heads, s.norm_eps, proj.dtype)
         return linear(self.runtime, mixed, self.out_w, residual=residual, out_dtype=residual.dtype, out=residual)

@@ -52,6 +52,11 @@ def test_heads_are_normed_and_rotated_in_one_pass(dim, dims, kv_heads, normed, d
 
 # ------------------------------------------------------------------ retention
 
+def new_state(n_slots, H, dk, dv, fill=0.0):
+    from damendaemon_b200 import kernels
+    return torch.full((n_slots, *kernels.retention_state_shape(H, dk, dv)), fill, device=DEV)
+
+
 def run_retention(q, k, v, lengths, slots, decay, key_scale, state, dims, base, dtype, interleaved=False):
     """One launch over entries of the given lengths (rows side by side) whose requests sit in the given slots and have
     state['pos'][slot] tokens behind them already."""
@@ -64,7 +69,7 @@ def run_retention(q, k, v, lengths, slots, decay, key_scale, state, dims, base, 
     qd, kd, vd = buf.split([q.shape[1], k.shape[1], v.shape[1]], dim=1)
     freqs = None if not dims else (base ** (-2.0 * torch.arange(dims // 2, dtype=torch.float64) / dims)).float().to(DEV)
     out = kernels.retention(qd, kd, vd, positions.to(DEV), i32(starts), i32(slots), torch.tensor(decay, dtype=torch.float32, device=DEV),
-                            key_scale, state["S"], freqs=freqs, interleaved=interleaved)
+                            key_scale, state["S"], q.shape[1] // len(decay), v.shape[1] // len(decay), freqs=freqs, interleaved=interleaved)
     assert kernels.read_error_flag(DEV) == 0
     for s, n in zip(slots, lengths):
         state["pos"][s] += n
@@ -90,7 +95,7 @@ def test_retention_in_portions_against_the_recurrence(H, dk, dv, dims, decay, dt
             pos = torch.arange(n)
             q64, k64 = plain.rotate_halves(q64, pos, dims, 300.0), plain.rotate_halves(k64, pos, dims, 300.0)
         want.append(plain.retention_recurrence(q64, k64 * scale, v64, torch.tensor(decay, dtype=torch.float64))[0].reshape(n, H * dv))
-    state = {"S": torch.full((n_slots, H, dv, dk), float("nan"), device=DEV), "pos": [0] * n_slots}
+    state = {"S": new_state(n_slots, H, dk, dv, float("nan")), "pos": [0] * n_slots}
     for s in slots:
         state["S"][s].zero_()                                  # what taking a slot does
     at = [0] * 4
@@ -112,7 +117,7 @@ def test_retention_in_portions_against_the_recurrence(H, dk, dv, dims, decay, dt
 def test_a_slot_taken_again_starts_from_zero_and_a_prompt_equals_its_tokens_one_by_one():
     H, dk, dv, n = 2, 32, 48, 70
     q, k, v = rnd(n, H * dk, seed=1), rnd(n, H * dk, seed=2), rnd(n, H * dv, seed=3)
-    state = {"S": torch.zeros((2, H, dv, dk), device=DEV), "pos": [0, 0]}
+    state = {"S": new_state(2, H, dk, dv), "pos": [0, 0]}
     whole, _ = run_retention(q, k, v, [n], [1], [0.9, 0.99], 0.2, state, 16, 100.0, torch.float32)
     kept = state["S"][1].clone()
     # the same slot again, as a new request: zeroed, then token by token
@@ -136,10 +141,10 @@ def test_a_marked_token_far_back_reaches_the_read_out_through_the_state(decay):
     k[far, 0], q[n - 1, :] = 7.0, 0.0
     q[n - 1, 0] = 3.0
     want = v[far].double() * 21.0 * decay ** (n - 1 - far)
-    state = {"S": torch.zeros((1, H, dv, dk), device=DEV), "pos": [0]}
+    state = {"S": new_state(1, H, dk, dv), "pos": [0]}
     whole, _ = run_retention(q, k, v, [n], [0], [decay], 1.0, state, 0, 1.0, torch.float32)
     assert (whole[n - 1] - want).abs().max() < 2e-4 * want.abs().max()
-    state = {"S": torch.zeros((1, H, dv, dk), device=DEV), "pos": [0]}
+    state = {"S": new_state(1, H, dk, dv), "pos": [0]}
     run_retention(q[:n - 30], k[:n - 30], v[:n - 30], [n - 30], [0], [decay], 1.0, state, 0, 1.0, torch.float32)
     for t in range(n - 30, n):
         last, _ = run_retention(q[t:t + 1], k[t:t + 1], v[t:t + 1], [1], [0], [decay], 1.0, state, 0, 1.0, torch.float32)
@@ -199,30 +204,37 @@ def test_the_dense_gated_feed_forward(width, inner, tokens, dtype):
     assert (got.cpu().double() - want).abs().max() < (2e-5 if dtype == torch.float32 else 0.05)
 
 
+@pytest.mark.parametrize("dtype,width", [(torch.float32, 64), (torch.bfloat16, 256), (torch.float32, 99), (torch.bfloat16, 100)])
 @pytest.mark.parametrize("experts,top,groups,keep", [(8, 2, 4, 2), (16, 3, 2, 1), (6, 2, 3, 1), (5, 1, 1, 1), (6, 2, 6, 2), (3, 3, 1, 1),
                                                      (64, 6, 8, 3), (12, 4, 4, 4)])
-def test_the_router_chooses_within_the_worthiest_groups(experts, top, groups, keep):
+def test_the_router_chooses_within_the_worthiest_groups(experts, top, groups, keep, dtype, width):
     from damendaemon_b200 import kernels
     tokens = 300
-    logits = rnd(tokens, experts + 1, seed=experts + top, scale=2.0)
-    scores = torch.sigmoid(logits[:, :experts].double())
+    y = rnd(tokens, width + (3 if width % 8 else 0), seed=experts + top, scale=1.0).to(dtype)[:, :width]      # odd widths: a padded row stride too
+    router = rnd(experts + 1, width, seed=experts, scale=2.0 * width ** -0.5).to(dtype)
+    logits = y.double() @ router.double().T
+    scores = torch.sigmoid(logits[:, :experts])
     want = plain.choose_experts(scores, top, groups, keep)
-    chosen, weight, shared = kernels.route_by_score(logits.to(DEV), experts, top, groups, keep, 2.5, gate_col=experts)
+    chosen, weight, shared = kernels.route_by_score(y.to(DEV), router.to(DEV), experts, top, groups, keep, 2.5, shared_gate=True)
     assert torch.equal(chosen.cpu().long(), want)
-    assert (weight.cpu().double() - 2.5 * scores.gather(1, want)).abs().max() < 1e-6
-    assert (shared.cpu().double() - torch.sigmoid(logits[:, experts].double())).abs().max() < 1e-6
-    # one group holds every expert: the plain top scores
-    chosen, _, none = kernels.route_by_score(logits.to(DEV), experts, top, 1, 1, 1.0)
+    assert (weight.cpu().double() - 2.5 * scores.gather(1, want)).abs().max() < 2e-6
+    assert (shared.cpu().double() - torch.sigmoid(logits[:, experts])).abs().max() < 2e-6
+    # one group holds every expert: the plain top scores; and no shared unit
+    chosen, _, none = kernels.route_by_score(y.to(DEV), router[:experts].to(DEV), experts, top, 1, 1, 1.0)
     assert none is None and torch.equal(chosen.cpu().long(), scores.topk(top, dim=-1).indices)
 
 
 def test_a_group_wins_by_its_two_best_and_loses_its_best_expert_with_it():
     """The largest single score lies in a group whose second score is small: with one group kept, that expert is not chosen."""
     from damendaemon_b200 import kernels
-    logits = torch.tensor([[4.0, -6.0, -6.0, 1.0, 1.5, -6.0]])
-    chosen, weight, _ = kernels.route_by_score(logits.to(DEV), 6, 2, 2, 1, 1.0)
+    router = torch.zeros(6, 8)
+    router[:, 0] = torch.tensor([4.0, -6.0, -6.0, 1.0, 1.5, -6.0])
+    y = torch.zeros(1, 8)
+    y[0, 0] = 1.0
+    chosen, weight, _ = kernels.route_by_score(y.to(DEV), router.to(DEV), 6, 2, 2, 1, 1.0)
     assert chosen.cpu().tolist() == [[4, 3]]
-    chosen, _, _ = kernels.route_by_score(logits.to(DEV), 6, 2, 2, 2, 1.0)
+    assert weight.cpu()[0, 0].item() == pytest.approx(torch.sigmoid(torch.tensor(1.5)).item(), abs=1e-6)
+    chosen, _, _ = kernels.route_by_score(y.to(DEV), router.to(DEV), 6, 2, 2, 2, 1.0)
     assert chosen.cpu().tolist() == [[0, 4]]
 
 
