@@ -117,35 +117,35 @@ template <> struct RoutePiece<__nv_bfloat16> {
     }
 };
 
-// One warp per token. First the router's logits, float32 sums of exact products: a lane sums the pieces lane, lane + 32,
-// ... of the row against eight router rows at a time (the token's row comes from L1 again for the next eight), the
-// lanes' sums are added in a fixed tree, so a token's logits do not depend on what else is in the step. Then the
-// scores of the E experts in shared memory; a run's worth by the lanes (a run each); the worthiest runs and then the
-// best experts by repeated arg-max over the warp, the lowest index winning a tie.
+// A block per token. First the router's logits, float32 sums of exact products: the block's four warps share the row's
+// columns out (piece w * 32 + lane, then every 128th), each lane sums its pieces against seventeen router rows at a time
+// (their loads are in flight together), a warp's lanes are added in a fixed tree and the four warps' sums in warp order,
+// so a token's logits do not depend on what else is in the step. Then the first warp: the scores of the E experts in
+// shared memory; a run's worth by the lanes (a run each); the worthiest runs and then the best experts by repeated
+// arg-max over the warp, the lowest index winning a tie.
 template <typename T>
 __global__ void __launch_bounds__(128)
 route_by_score_kernel(const T* __restrict__ y, int ldy, const T* __restrict__ router, int ldr, int width, int n_tokens,
                       int n_experts, int top, int groups, int keep, float weight_scale, int gate_row,
                       int* __restrict__ chosen, float* __restrict__ pair_weight, float* __restrict__ shared_scale) {
-    extern __shared__ float route_smem[];        // per warp: [E] scores, [groups] worths
+    extern __shared__ float route_smem[];        // [E] scores, [groups] worths, [4][rows] the warps' sums
     dd_launch_dependents();
     dd_grid_wait();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x * 4 + warp;
-    if (t >= n_tokens) return;
-    float* score = route_smem + warp * (n_experts + groups);
-    float* worth = score + n_experts;
-    const T* x = y + (size_t)t * ldy;
-    constexpr int V = RoutePiece<T>::N, ROWS = 8;
-    const bool wide = width % V == 0 && ldy % V == 0 && ldr % V == 0 && !(((uintptr_t)y | (uintptr_t)router) & 15);
+    const int t = blockIdx.x;
     const int n_rows = n_experts + (gate_row >= 0 ? 1 : 0);          // the shared unit's gate vector is one more row
-    float gate_logit = 0.f;
+    float* score = route_smem;
+    float* worth = score + n_experts;
+    float* part = worth + groups;
+    const T* x = y + (size_t)t * ldy;
+    constexpr int V = RoutePiece<T>::N, ROWS = 17;       // sixteen experts and a shared unit's gate in one pass
+    const bool wide = width % V == 0 && ldy % V == 0 && ldr % V == 0 && !(((uintptr_t)y | (uintptr_t)router) & 15);
     for (int e0 = 0; e0 < n_rows; e0 += ROWS) {
         float acc[ROWS];
 #pragma unroll
         for (int j = 0; j < ROWS; ++j) acc[j] = 0.f;
         if (wide) {
-            for (int c = lane * V; c < width; c += 32 * V) {
+            for (int c = (warp * 32 + lane) * V; c < width; c += 128 * V) {
                 float xv[V];
                 RoutePiece<T>::load(x + c, xv);
 #pragma unroll
@@ -158,7 +158,7 @@ route_by_score_kernel(const T* __restrict__ y, int ldy, const T* __restrict__ ro
                 }
             }
         } else {
-            for (int c = lane; c < width; c += 32) {
+            for (int c = warp * 32 + lane; c < width; c += 128) {
                 const float xv = dd_to_f32(x[c]);
 #pragma unroll
                 for (int j = 0; j < ROWS; ++j)
@@ -168,11 +168,19 @@ route_by_score_kernel(const T* __restrict__ y, int ldy, const T* __restrict__ ro
 #pragma unroll
         for (int j = 0; j < ROWS; ++j) {
             const float z = dd_warp_sum(acc[j]);
-            if (e0 + j < n_experts) { if (lane == 0) score[e0 + j] = 1.0f / (1.0f + expf(-z)); }
-            else if (e0 + j == gate_row) gate_logit = z;
+            if (lane == 0 && e0 + j < n_rows) part[warp * n_rows + e0 + j] = z;
         }
     }
-    if (lane == 0 && shared_scale) shared_scale[t] = gate_row >= 0 ? 1.0f / (1.0f + expf(-gate_logit)) : 1.0f;
+    __syncthreads();
+    for (int e = threadIdx.x; e < n_rows; e += 128) {
+        const float z = ((part[e] + part[n_rows + e]) + part[2 * n_rows + e]) + part[3 * n_rows + e];
+        const float s = 1.0f / (1.0f + expf(-z));
+        if (e < n_experts) score[e] = s;
+        else if (shared_scale) shared_scale[t] = s;
+    }
+    if (threadIdx.x == 0 && shared_scale && gate_row < 0) shared_scale[t] = 1.0f;
+    __syncthreads();
+    if (warp) return;
     __syncwarp();
     const int per = n_experts / groups;
     if (groups > 1) {
@@ -351,10 +359,10 @@ DD_API int dd_route_by_score(const void* y, int ldy, const void* router, int ldr
     if (n_experts <= 0 || top <= 0 || top > n_experts || groups <= 0 || n_experts % groups || keep <= 0 || keep > groups ||
         (gate_row >= 0 && gate_row != n_experts) || width <= 0)
         return dd_fail("dd_route_by_score: %d of %d experts in %d groups of which %d stay, gate row %d", top, n_experts, groups, keep, gate_row);
-    const size_t smem = 4 * (size_t)(n_experts + groups) * sizeof(float);
-    if (smem > 48 * 1024) return dd_fail("dd_route_by_score: %d experts are more than a warp's shared memory holds", n_experts);
+    const size_t smem = (size_t)(n_experts + groups + 4 * (n_experts + 1)) * sizeof(float);
+    if (smem > 48 * 1024) return dd_fail("dd_route_by_score: %d experts are more than a block's shared memory holds", n_experts);
     cudaStream_t s = (cudaStream_t)stream;
-    const dim3 grid(dd_ceil_div(n_tokens, 4));
+    const dim3 grid(n_tokens);
     if (dtype == DD_F32)
         dd_launch(route_by_score_kernel<float>, grid, dim3(128), smem, s, (const float*)y, ldy, (const float*)router, ldr, width,
                   n_tokens, n_experts, top, groups, keep, weight_scale, gate_row, chosen, pair_weight, shared_scale);

@@ -146,8 +146,8 @@ retention_kernel(const T* __restrict__ q, const T* __restrict__ k, const T* __re
     auto request = [&](int base, float* buffer) {             // PREPARED: a chunk's tokens by 16-byte copies
         const int n = min(a.chunk, t1 - base);
         const int q_pieces = a.dkp / 4, pieces = 2 * q_pieces + (COLS + 3) / 4;
-        // the first warp asks for the whole chunk (the others would walk the same loop for nothing)
-        for (int tt = 0; warp == 0 && tt < n; ++tt) {
+        // a warp asks for every WARPS-th token of the chunk, a lane for every 32nd piece of it
+        for (int tt = warp; tt < n; tt += WARPS) {
             const float* src = a.prepared + ((size_t)(base + tt) * a.heads + h) * prepared_row;
             float* dst = buffer + tt * PER_TOKEN;
             for (int piece = lane; piece < pieces; piece += 32) {
